@@ -1,0 +1,269 @@
+"""Distributed 3D SDDMM and SpMM.
+
+One object per (plan, k, dtype, variant).  The plan is built once per
+(matrix, mesh); an op built from it is run many times, like the reference's
+"setup once, iterate" contract (miniapp/bench_both.cpp:172-236,
+miniapp/bench_spmm.cpp:166-188).
+
+    C = S o (A B^T)        DistSDDMM   (src/distributed_comp.cpp:141-284, 349-413)
+    Y = S X                DistSpMM    (src/distributed_comp.cpp:17-76, 285-348)
+
+Dense operands live in *owner layout*: rank (x, y, z) holds the rows it owns
+(`plan.row.owned_gids` for A / Y, `plan.col.owned_gids` for B / X) and the
+z-th slice of the k columns.  Variants:
+
+  "sparse"     packed exchange with send and receive staging   (ref "sparse")
+  "sparseNRB"  packed exchange, received rows land in place    (ref "sparseNRB")
+  "fused"      one sm_100a kernel per op that pulls the needed rows from the
+               owners' memory over NVLink, computes, and pushes partial
+               results to their owners (zero staging; the role of ref
+               "sparseNB"); needs GPUs with peer access
+  "dense"      sparsity-agnostic: all-gather whole slabs, reduce-scatter
+               (ref "dense", src/dcomm_setup.cpp)
+
+SDDMM result: after the Z reduction fiber rank z holds the z-th contiguous
+slice of the block's values in the plan's CSR order.  SpMM result: owned rows
+of Y; partial rows are summed at the owner in ascending peer order.  (The
+reference's sparse SpMM post step sends a stale buffer,
+src/distributed_comp.cpp:59; here it is defined by the math.)
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..ops import local
+from ..parallel.comm import DenseExchange, FiberReduce, PhaseTimer, SparseExchange
+from ..parallel.mesh import MeshGroups, split_k
+from ..parallel.plan import RankPlan
+from ..utils import generate
+
+VARIANTS = ("sparse", "sparseNRB", "fused", "dense")
+ALG_NAMES = {"sparse": "sparse", "sparseNRB": "sparseNRB", "fused": "sparseNB", "dense": "dense"}
+
+
+class _Dist3DOp:
+    kernel = "?"
+
+    def __init__(self, plan: RankPlan, groups: MeshGroups | None, k: int, dtype=torch.float32,
+                 device="cpu", variant: str = "sparseNRB"):
+        if variant not in VARIANTS:
+            raise ValueError(f"variant must be one of {VARIANTS}")
+        self.plan, self.groups, self.k, self.dtype, self.variant = plan, groups, k, dtype, variant
+        self.device = torch.device(device)
+        self.mesh = plan.mesh
+        self.k_off, self.k_loc = split_k(k, self.mesh.Z, plan.coords[2])
+        self.timer = PhaseTimer(self.device)
+        self.last_times: dict = {}
+        if groups is None and self.mesh.size != 1:
+            raise ValueError("a multi-rank mesh needs MeshGroups")
+        if variant == "fused" and self.device.type != "cuda":
+            raise ValueError("the fused variant runs on GPUs only")
+        self.rowptr = torch.from_numpy(plan.rowptr).to(self.device)
+        self.vals = torch.from_numpy(plan.vals).to(device=self.device, dtype=dtype)
+        rowidx, colidx = plan.rowidx, plan.colidx
+        self._row_group = groups.row if groups else None
+        self._col_group = groups.col if groups else None
+        self._fiber_group = groups.fiber if groups else None
+        self._dense_row = self._dense_col = None
+        if variant == "dense":
+            self._dense_row = DenseExchange(plan.row, self._row_group, self.k_loc, dtype, self.device)
+            self._dense_col = DenseExchange(plan.col, self._col_group, self.k_loc, dtype, self.device)
+            rowidx = self._dense_row.slab_index()[rowidx].astype(np.int32)
+            colidx = self._dense_col.slab_index()[colidx].astype(np.int32)
+        self.rowidx = torch.from_numpy(np.ascontiguousarray(rowidx)).to(self.device)
+        self.colidx = torch.from_numpy(np.ascontiguousarray(colidx)).to(self.device)
+
+    # ---- helpers ---------------------------------------------------------
+    def _alloc_local(self, side):
+        return torch.zeros(side.n_local, self.k_loc, dtype=self.dtype, device=self.device)
+
+    def _exchange(self, side, group):
+        mode = "buffered" if self.variant == "sparse" else "nrb"
+        return SparseExchange(side, group, self.k_loc, self.dtype, self.device, mode, self.timer)
+
+    def fill_owned(self, target: torch.Tensor, gids, *, kind=generate.FILL_NORMAL, const=0.0, seed=0, stream=0):
+        """Writes rows `gids`, my k slice, of the virtual global operand
+        defined by (seed, stream) into `target`."""
+        npdt = np.float32 if self.dtype == torch.float32 else np.float64
+        host = generate.fill_rows(gids, self.k, self.k_off, self.k_loc, kind=kind, const=const, seed=seed,
+                                  stream=stream, dtype=npdt)
+        target.copy_(torch.from_numpy(host))
+        return target
+
+    def poison_unowned(self):
+        """NaN-fills every non-owned row so a missed transfer shows up."""
+        for buf, side in self._local_buffers():
+            buf[side.n_owned:].fill_(float("nan"))
+
+    def _finish(self):
+        self.last_times = self.timer.collect()
+        t = self.last_times
+        t["total"] = t.get("comm1", 0.0) + t.get("comp", 0.0) + t.get("comm2", 0.0)
+        return t
+
+    def alg_name(self, phase: str) -> str:
+        return f"{ALG_NAMES[self.variant]} {self.kernel} {phase}"
+
+
+class DistSDDMM(_Dist3DOp):
+    kernel = "sddmm"
+
+    def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
+        super().__init__(plan, groups, k, dtype, device, variant)
+        p = plan
+        if variant == "fused":
+            from ..ops.fused import FusedSDDMM
+            self._fused = FusedSDDMM(self, **kw)
+            self.A_loc, self.B_loc = self._fused.A_loc, self._fused.B_loc
+        else:
+            self.A_loc, self.B_loc = self._alloc_local(p.row), self._alloc_local(p.col)
+        self.A_owned, self.B_owned = self.A_loc[:p.row.n_owned], self.B_loc[:p.col.n_owned]
+        self.partial = torch.zeros(p.nnz, dtype=dtype, device=self.device)
+        if variant in ("sparse", "sparseNRB"):
+            self.exA = self._exchange(p.row, self._row_group)
+            self.exB = self._exchange(p.col, self._col_group)
+        if variant != "fused":
+            self.fiber = FiberReduce(p.nnz, self.mesh.Z, p.coords[2], self._fiber_group, dtype, self.device)
+        self.owned_off, self.owned_len = p.owned_nnz_slice()
+
+    def _local_buffers(self):
+        return [(self.A_loc, self.plan.row), (self.B_loc, self.plan.col)]
+
+    def run(self) -> torch.Tensor:
+        """One distributed SDDMM; returns my slice of C's values."""
+        t = self.timer
+        if self.variant == "fused":
+            with t.span("comp"):
+                c = self._fused.run()
+        elif self.variant == "dense":
+            with t.span("comm1"):
+                A = self._dense_row.all_gather(self.A_owned)
+                B = self._dense_col.all_gather(self.B_owned)
+            with t.span("comp"):
+                local.sddmm(self.rowidx, self.colidx, self.vals, A, B, out=self.partial)
+            with t.span("comm2"):
+                c = self.fiber(self.partial)
+        else:
+            with t.span("comm1"):
+                self.exA.expand(self.A_loc)
+                self.exB.expand(self.B_loc)
+            with t.span("comp"):
+                local.sddmm(self.rowidx, self.colidx, self.vals, self.A_loc, self.B_loc, out=self.partial)
+            with t.span("comm2"):
+                c = self.fiber(self.partial)
+        if self.mesh.Z == 1:
+            c = c[self.owned_off:self.owned_off + self.owned_len]
+        self._finish()
+        return c
+
+    def comm_stats(self):
+        """{'PRE': ((send_msgs, send_vol), (recv_msgs, recv_vol)), 'POST': ...}
+        in the reference's units (elements)."""
+        p, k = self.plan, self.k_loc
+        if self.variant == "dense":
+            (sa, ra), (sb, rb) = self._dense_row.stats_gather(), self._dense_col.stats_gather()
+            pre = ((1, sa[1] + sb[1]), (ra[0] + rb[0], ra[1] + rb[1]))
+        else:
+            s, r, sm, rm = p.expand_rows()
+            pre = ((sm, s * k), (rm, r * k))
+        from ..parallel.mesh import split_nnz
+        post = ((1, p.nnz), (1, split_nnz(p.nnz, self.mesh.Z, p.coords[2])[1]))
+        return {"PRE": pre, "POST": post}
+
+    def flops(self) -> float:
+        return 2.0 * self.plan.gnnz * self.k
+
+
+class DistSpMM(_Dist3DOp):
+    kernel = "spmm"
+
+    def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
+        super().__init__(plan, groups, k, dtype, device, variant)
+        p = plan
+        if variant == "fused":
+            from ..ops.fused import FusedSpMM
+            self._fused = FusedSpMM(self, **kw)
+            self.X_loc, self.Y_loc = self._fused.X_loc, self._fused.Y_loc
+        else:
+            self.X_loc, self.Y_loc = self._alloc_local(p.col), self._alloc_local(p.row)
+        self.X_owned = self.X_loc[:p.col.n_owned]
+        self.Y_owned = torch.zeros(p.row.n_owned, self.k_loc, dtype=dtype, device=self.device)
+        self.sched = None
+        if variant in ("sparse", "sparseNRB"):
+            self.exX = self._exchange(p.col, self._col_group)
+            self.exY = self._exchange(p.row, self._row_group)
+        if variant == "dense":
+            self._Yslab = torch.zeros(p.row.npeers * self._dense_row.max_owned, self.k_loc, dtype=dtype,
+                                      device=self.device)
+            # CSR over slab rows for the local kernel
+            order = np.argsort(self.rowidx.cpu().numpy(), kind="stable")
+            ri = self.rowidx.cpu().numpy()[order]
+            self._d_rowidx = torch.from_numpy(ri).to(self.device)
+            self._d_colidx = self.colidx[torch.from_numpy(order).to(self.device)]
+            self._d_vals = self.vals[torch.from_numpy(order).to(self.device)]
+            rp = np.zeros(self._Yslab.shape[0] + 1, np.int64)
+            np.cumsum(np.bincount(ri, minlength=self._Yslab.shape[0]), out=rp[1:])
+            self._d_rowptr = torch.from_numpy(rp).to(self.device)
+            self._d_sched = None
+        if self.device.type == "cuda" and variant != "fused":
+            from ..ops import cuda_ops
+            if variant == "dense":
+                self._d_sched = cuda_ops.SpmmSchedule(self._d_rowptr)
+            else:
+                self.sched = cuda_ops.SpmmSchedule(self.rowptr)
+
+    def _local_buffers(self):
+        return [(self.X_loc, self.plan.col)]
+
+    def run(self, beta: float = 0.0) -> torch.Tensor:
+        """One distributed SpMM: Y_owned = beta*Y_owned + (S X)[owned rows]."""
+        t, p = self.timer, self.plan
+        if self.variant == "fused":
+            with t.span("comp"):
+                self._fused.run(self.Y_owned, beta)
+        elif self.variant == "dense":
+            with t.span("comm1"):
+                X = self._dense_col.all_gather(self.X_owned)
+            with t.span("comp"):
+                local.spmm(self._d_rowptr, self._d_rowidx, self._d_colidx, self._d_vals, X, self._Yslab, 0.0,
+                           self._d_sched)
+            with t.span("comm2"):
+                if beta == 0.0:
+                    self._dense_row.reduce_scatter(self._Yslab, self.Y_owned)
+                else:
+                    prev = self.Y_owned * beta
+                    self._dense_row.reduce_scatter(self._Yslab, self.Y_owned)
+                    self.Y_owned += prev
+        else:
+            with t.span("comm1"):
+                self.exX.expand(self.X_loc)
+            with t.span("comp"):
+                local.spmm(self.rowptr, self.rowidx, self.colidx, self.vals, self.X_loc, self.Y_loc, 0.0,
+                           self.sched)
+            with t.span("comm2"):
+                self.exY.reduce(self.Y_loc)
+                if beta == 0.0:
+                    self.Y_owned.copy_(self.Y_loc[:p.row.n_owned])
+                else:
+                    self.Y_owned.mul_(beta).add_(self.Y_loc[:p.row.n_owned])
+        self._finish()
+        return self.Y_owned
+
+    def comm_stats(self):
+        p, k = self.plan, self.k_loc
+        if self.variant == "dense":
+            pre = self._dense_col.stats_gather()
+            mo = self._dense_row.max_owned
+            allv = int(p.row.peer_owned.sum()) * k
+            post = ((1, allv), (1, int(p.row.peer_owned[p.row.me]) * k))
+        else:
+            s, r, sm, rm = p.expand_rows(("col",))
+            pre = ((sm, s * k), (rm, r * k))
+            # reduce = expand of the row side with roles swapped (src/comm_setup.cpp:778-784)
+            s, r, sm, rm = p.expand_rows(("row",))
+            post = ((rm, r * k), (sm, s * k))
+        return {"PRE": pre, "POST": post}
+
+    def flops(self) -> float:
+        return 2.0 * self.plan.gnnz * self.k

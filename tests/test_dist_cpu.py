@@ -1,0 +1,82 @@
+"""Distributed CPU plumbing: gloo ranks, fp64, every variant against the
+single-process oracle, with non-owned rows poisoned before each run."""
+import numpy as np
+import pytest
+import torch
+
+from dist_utils import run_ranks
+
+K = 32
+
+
+def _check_rank(rank, world, meshstr, kernel, variant, k, from_file):
+    from spcomm3d_b200.models.dist_ops import DistSDDMM, DistSpMM
+    from spcomm3d_b200.ops import oracle
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups, split_k
+    from spcomm3d_b200.parallel.partition import distribute_from_file
+    from spcomm3d_b200.parallel.plan import build_my_plan, build_rank_plan
+    from spcomm3d_b200.utils import generate
+    from spcomm3d_b200.utils.sparse import CooMatrix
+
+    mesh = Mesh3D.parse(meshstr)
+    groups = MeshGroups.create(mesh)
+    M, N = 384, 320
+    m = generate.fixed_degree(M, N, 6, seed=11)
+    if from_file:
+        block, directory = distribute_from_file(from_file, mesh, groups, seed=7)
+        plan = build_rank_plan(block, directory, groups.coords, gnnz=m.nnz)
+    else:
+        directory, plan = build_my_plan(m, mesh, rank, seed=7)
+    plan.validate()
+    directory.check()
+    A = generate.fill_rows(np.arange(M), k, 0, k, seed=5, stream=1, dtype=np.float64)
+    B = generate.fill_rows(np.arange(N), k, 0, k, seed=5, stream=2, dtype=np.float64)
+    z = groups.coords[2]
+    if kernel == "sddmm":
+        op = DistSDDMM(plan, groups, k, torch.float64, "cpu", variant)
+        op.fill_owned(op.A_owned, plan.row.owned_gids, seed=5, stream=1)
+        op.fill_owned(op.B_owned, plan.col.owned_gids, seed=5, stream=2)
+        for _ in range(2):
+            op.poison_unowned()
+            c = op.run()
+        off, ln = plan.owned_nnz_slice()
+        mine = CooMatrix(M, N, plan.global_rows()[off:off + ln], plan.global_cols()[off:off + ln],
+                         plan.vals[off:off + ln])
+        ref = oracle.sddmm_ref(mine, A, B)
+        assert c.shape[0] == ln
+        torch.testing.assert_close(c, ref, rtol=1e-12, atol=1e-12)
+    else:
+        op = DistSpMM(plan, groups, k, torch.float64, "cpu", variant)
+        op.fill_owned(op.X_owned, plan.col.owned_gids, seed=5, stream=2)
+        for _ in range(2):
+            op.poison_unowned()
+            y = op.run()
+        ko, kl = split_k(k, mesh.Z, z)
+        ref = oracle.spmm_ref(m, B)[plan.row.owned_gids][:, ko:ko + kl]
+        torch.testing.assert_close(y, ref, rtol=1e-12, atol=1e-12)
+
+
+def _check_many(rank, world, meshstr, cases, k, from_file):
+    for kernel, variant in cases:
+        _check_rank(rank, world, meshstr, kernel, variant, k, from_file)
+
+
+def test_2x2x2_all_variants():
+    cases = [(kern, var) for kern in ("sddmm", "spmm") for var in ("sparse", "sparseNRB", "dense")]
+    run_ranks(_check_many, 8, "2x2x2", cases, K, None)
+
+
+@pytest.mark.parametrize("meshstr,k", [("4x2x1", 32), ("1x1x8", 20), ("2x1x2", 7), ("1x3x1", 16), ("3x1x1", 16)])
+def test_other_meshes(meshstr, k):
+    from spcomm3d_b200.parallel.mesh import Mesh3D
+    n = Mesh3D.parse(meshstr).size
+    run_ranks(_check_many, n, meshstr, [("sddmm", "sparseNRB"), ("spmm", "sparseNRB"), ("sddmm", "dense"),
+                                        ("spmm", "dense")], k, None)
+
+
+def test_distributed_reader(tmp_path):
+    from spcomm3d_b200.utils import binfmt, generate
+    m = generate.fixed_degree(384, 320, 6, seed=11)
+    path = str(tmp_path / "m.bin")
+    binfmt.write_bin(path, m)
+    run_ranks(_check_many, 8, "2x2x2", [("sddmm", "sparseNRB"), ("spmm", "sparse")], K, path)
