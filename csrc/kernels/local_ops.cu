@@ -1,0 +1,531 @@
+// Local (one GPU, no communication) kernels for sm_100a:
+//   SDDMM over a row-sorted nonzero list, SpMM over scheduled work items,
+//   row gather / scatter / scatter-add, operand fill, checksum, index remaps.
+//
+// They replace the scalar CPU loops of the reference: sddmm / spmm
+// src/core_ops.cpp:5-35, pack / unpack / sum src/comm.hpp:90-103,166-189,
+// ReMapIndices src/SparseMatrix.hpp:100-106, checksum
+// miniapp/bench_spmm.cpp:117.
+//
+// Layout of the math: a dense row of k elements is spread over a group of G
+// lanes (G = power of two <= 32), each lane holding R 16-byte vectors, so one
+// warp works on 32/G nonzeros (SDDMM) or rows (SpMM) at a time and every
+// global access is a full-width vector load of a contiguous row segment.
+// Both kernels are bound by the gathers of dense rows from HBM/L2; the
+// unroll factor U keeps U independent row loads in flight per lane.
+#include "sp3_cuda.cuh"
+
+namespace sp3 {
+
+constexpr int SDDMM_U = 4;
+constexpr int SPMM_U = 4;
+
+// ---------------------------------------------------------------------------
+// SDDMM: out[i] = sval[i] * <A[rowidx[i]], B[colidx[i]]>
+// Each lane group walks `per_slot` consecutive nonzeros; since the list is
+// sorted by row, the A row stays in registers until the row changes.
+// ---------------------------------------------------------------------------
+template <typename T, int G, int R>
+__global__ void __launch_bounds__(256)
+sddmm_vec_kernel(long long nnz, const int* __restrict__ rowidx, const int* __restrict__ colidx,
+                 const T* __restrict__ sval, const T* __restrict__ A, long long lda,
+                 const T* __restrict__ B, long long ldb, int nvec, T* __restrict__ out, int per_slot) {
+    using V = typename Vec<T>::type;
+    constexpr int SLOTS = 32 / G;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31, slot = lane / G, gl = lane % G;
+    const long long begin = (warp * SLOTS + slot) * (long long)per_slot;
+    const long long end = begin + per_slot < nnz ? begin + per_slot : nnz;
+    const V* Av = reinterpret_cast<const V*>(A);
+    const V* Bv = reinterpret_cast<const V*>(B);
+    const long long lda_v = lda / Vec<T>::N, ldb_v = ldb / Vec<T>::N;
+    int cur_row = -1;
+    V a[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) a[r] = vzero((V*)nullptr);
+    for (int it = 0; it < per_slot; it += SDDMM_U) {
+        int rr[SDDMM_U], cc[SDDMM_U];
+        V b[SDDMM_U][R];
+#pragma unroll
+        for (int u = 0; u < SDDMM_U; ++u) {
+            const long long i = begin + it + u;
+            const bool ok = i < end;
+            rr[u] = ok ? __ldg(rowidx + i) : -1;
+            cc[u] = ok ? __ldg(colidx + i) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < SDDMM_U; ++u)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int v = gl + r * G;
+                b[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Bv + (long long)cc[u] * ldb_v + v) : vzero((V*)nullptr);
+            }
+#pragma unroll
+        for (int u = 0; u < SDDMM_U; ++u) {
+            if (rr[u] >= 0 && rr[u] != cur_row) {
+                cur_row = rr[u];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int v = gl + r * G;
+                    a[r] = v < nvec ? __ldg(Av + (long long)cur_row * lda_v + v) : vzero((V*)nullptr);
+                }
+            }
+            T acc = 0;
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc += vdot(a[r], b[u][r]);
+#pragma unroll
+            for (int m = G / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+            const long long i = begin + it + u;
+            if (gl == 0 && i < end) out[i] = sval ? acc * __ldg(sval + i) : acc;
+        }
+    }
+}
+
+// Any k, any leading dimension: one warp per nonzero slot, scalar loads.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sddmm_scalar_kernel(long long nnz, const int* __restrict__ rowidx, const int* __restrict__ colidx,
+                    const T* __restrict__ sval, const T* __restrict__ A, long long lda,
+                    const T* __restrict__ B, long long ldb, int k, T* __restrict__ out) {
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long i = warp; i < nnz; i += nwarps) {
+        const T* a = A + (long long)rowidx[i] * lda;
+        const T* b = B + (long long)colidx[i] * ldb;
+        T acc = 0;
+        for (int j = lane; j < k; j += 32) acc += a[j] * b[j];
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        if (lane == 0) out[i] = sval ? acc * sval[i] : acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// SpMM over work items (one warp per item).
+//   rows item   {row_begin, row_end, 0, -1}: lane groups take whole rows.
+//   piece item  {row, nnz_begin, nnz_end, long_row_slot}: a slice of a long
+//               row; the warp's partial goes to the carry scratch and the
+//               warp that completes the row adds the pieces in piece order
+//               (fixed order => bitwise reproducible) and writes the row.
+// Y[row] = beta * Y[row] + sum.  Rows without nonzeros are covered by rows
+// items, so beta is applied to every row exactly once.
+// ---------------------------------------------------------------------------
+struct SpmmLong {
+    const int* first_piece;  // [nlong] first carry slot of each long row
+    const int* npieces;      // [nlong]
+    int* counters;           // [nlong] zero at launch; reset by the finishing warp
+    void* carry;             // [total pieces, ldc] scratch
+    long long ldc;           // elements per carry row
+    int piece_len;           // nonzeros per piece
+};
+
+template <typename T, int G, int R>
+__device__ __forceinline__ void spmm_accumulate(typename Vec<T>::type (&acc)[R], long long p0, long long p1, int stride,
+                                                const int* __restrict__ colidx, const T* __restrict__ val,
+                                                const typename Vec<T>::type* __restrict__ Xv, long long ldx_v,
+                                                int gl, int nvec) {
+    using V = typename Vec<T>::type;
+    for (long long p = p0; p < p1; p += (long long)SPMM_U * stride) {
+        int cc[SPMM_U];
+        T vv[SPMM_U];
+#pragma unroll
+        for (int u = 0; u < SPMM_U; ++u) {
+            const long long q = p + (long long)u * stride;
+            const bool ok = q < p1;
+            cc[u] = ok ? __ldg(colidx + q) : -1;
+            vv[u] = ok ? __ldg(val + q) : (T)0;
+        }
+        V x[SPMM_U][R];
+#pragma unroll
+        for (int u = 0; u < SPMM_U; ++u)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int v = gl + r * G;
+                x[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Xv + (long long)cc[u] * ldx_v + v) : vzero((V*)nullptr);
+            }
+#pragma unroll
+        for (int u = 0; u < SPMM_U; ++u)
+#pragma unroll
+            for (int r = 0; r < R; ++r) vfma(acc[r], vv[u], x[u][r]);
+    }
+}
+
+template <typename T, int G, int R>
+__global__ void __launch_bounds__(256)
+spmm_items_kernel(int nitems, const int4* __restrict__ items, const long long* __restrict__ rowptr,
+                  const int* __restrict__ colidx, const T* __restrict__ val, const T* __restrict__ X,
+                  long long ldx, int nvec, T beta, T* __restrict__ Y, long long ldy, SpmmLong lg) {
+    using V = typename Vec<T>::type;
+    constexpr int SLOTS = 32 / G;
+    const int warp = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    if (warp >= nitems) return;
+    const int lane = threadIdx.x & 31, slot = lane / G, gl = lane % G;
+    const int4 item = __ldg(items + warp);
+    const V* Xv = reinterpret_cast<const V*>(X);
+    V* Yv = reinterpret_cast<V*>(Y);
+    const long long ldx_v = ldx / Vec<T>::N, ldy_v = ldy / Vec<T>::N;
+    V acc[R];
+    if (item.w < 0) {
+        for (int row = item.x + slot; row < item.y; row += SLOTS) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] = vzero((V*)nullptr);
+            spmm_accumulate<T, G, R>(acc, rowptr[row], rowptr[row + 1], 1, colidx, val, Xv, ldx_v, gl, nvec);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int v = gl + r * G;
+                if (v < nvec) {
+                    V* y = Yv + (long long)row * ldy_v + v;
+                    if (beta != (T)0) { V o = vscale(beta, *y); vadd(o, acc[r]); *y = o; }
+                    else *y = acc[r];
+                }
+            }
+        }
+        return;
+    }
+    // piece of a long row: slots stride over the piece, then combine
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = vzero((V*)nullptr);
+    spmm_accumulate<T, G, R>(acc, (long long)item.y + slot, item.z, SLOTS, colidx, val, Xv, ldx_v, gl, nvec);
+#pragma unroll
+    for (int m = G; m < 32; m <<= 1)
+#pragma unroll
+        for (int r = 0; r < R; ++r) vadd(acc[r], shfl_xor_vec(acc[r], m));
+    const int lr = item.w, row = item.x;
+    const int first = __ldg(lg.first_piece + lr), np = __ldg(lg.npieces + lr);
+    const int piece = first + (int)((item.y - rowptr[row]) / lg.piece_len);
+    V* carry = reinterpret_cast<V*>(lg.carry);
+    const long long ldc_v = lg.ldc / Vec<T>::N;
+    if (slot == 0)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int v = gl + r * G;
+            if (v < nvec) __stcg(carry + (long long)piece * ldc_v + v, acc[r]);
+        }
+    __threadfence();
+    __syncwarp();
+    int old = 0;
+    if (lane == 0) old = atomicAdd(lg.counters + lr, 1);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old != np - 1) return;
+    __threadfence();
+    if (slot == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int v = gl + r * G;
+            if (v >= nvec) continue;
+            V s = vzero((V*)nullptr);
+            for (int j = 0; j < np; ++j) vadd(s, __ldcg(carry + (long long)(first + j) * ldc_v + v));
+            V* y = Yv + (long long)row * ldy_v + v;
+            if (beta != (T)0) { V o = vscale(beta, *y); vadd(o, s); *y = o; }
+            else *y = s;
+        }
+    }
+    if (lane == 0) lg.counters[lr] = 0;
+}
+
+// Any k / leading dimension: one warp per row, scalar loads, no schedule.
+template <typename T>
+__global__ void __launch_bounds__(256)
+spmm_scalar_kernel(int nrows, const long long* __restrict__ rowptr, const int* __restrict__ colidx,
+                   const T* __restrict__ val, const T* __restrict__ X, long long ldx, int k, T beta,
+                   T* __restrict__ Y, long long ldy) {
+    const int warp = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const int lane = threadIdx.x & 31;
+    if (warp >= nrows) return;
+    for (int j = lane; j < k; j += 32) {
+        T acc = 0;
+        for (long long p = rowptr[warp]; p < rowptr[warp + 1]; ++p) acc += val[p] * X[(long long)colidx[p] * ldx + j];
+        T* y = Y + (long long)warp * ldy + j;
+        *y = beta != (T)0 ? beta * *y + acc : acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// rows: mode 0 dst[i] = src[idx[i]]; 1 dst[idx[i]] = src[i]; 2 dst[idx[i]] += src[i]
+// ---------------------------------------------------------------------------
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+rows_kernel(int mode, long long n, const long long* __restrict__ idx, const T* __restrict__ src, long long lds,
+            T* __restrict__ dst, long long ldd, int k) {
+    using V = typename Vec<T>::type;
+    const int nvec = VEC ? k / Vec<T>::N : k;
+    const int G = pick_group(nvec);
+    const int lane = threadIdx.x & 31, slot = lane / G, gl = lane % G;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long i = warp * (32 / G) + slot;
+    if (i >= n) return;
+    const long long j = idx[i];
+    const long long srow = mode == 0 ? j : i, drow = mode == 0 ? i : j;
+    if (VEC) {
+        const V* s = reinterpret_cast<const V*>(src + srow * lds);
+        V* d = reinterpret_cast<V*>(dst + drow * ldd);
+        for (int v = gl; v < nvec; v += G) {
+            V x = __ldg(s + v);
+            if (mode == 2) { V o = d[v]; vadd(o, x); d[v] = o; }
+            else d[v] = x;
+        }
+    } else {
+        const T* s = src + srow * lds;
+        T* d = dst + drow * ldd;
+        for (int v = gl; v < nvec; v += G) {
+            if (mode == 2) d[v] += s[v];
+            else d[v] = s[v];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Operand fill: the device twin of sp3_fill_rows_* (csrc/host/generate.cpp).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ unsigned long long rnd(unsigned long long seed, unsigned long long stream,
+                                                  unsigned long long idx) {
+    return mix64(mix64(seed ^ (stream * 0xD6E8FEB86659FD93ull)) + idx * 0x9E3779B97F4A7C15ull);
+}
+__device__ __forceinline__ double u01(unsigned long long bits) {
+    return (double)(bits >> 11) * (1.0 / 9007199254740992.0);
+}
+
+template <typename T>
+__global__ void fill_rows_kernel(const long long* __restrict__ gid, long long nrows, long long col0, int ncols,
+                                 long long ld, long long kglobal, int kind, double cval,
+                                 unsigned long long seed, unsigned long long stream, T* __restrict__ out) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nrows * ncols) return;
+    const long long i = t / ncols;
+    const int j = (int)(t % ncols);
+    double v;
+    if (kind == 0) {
+        const unsigned long long e = (unsigned long long)gid[i] * (unsigned long long)kglobal + col0 + j;
+        double u1 = u01(rnd(seed, stream, 2 * e)), u2 = u01(rnd(seed, stream, 2 * e + 1));
+        if (u1 < 1e-300) u1 = 1e-300;
+        v = sqrt(-2.0 * log(u1)) * cos(6.283185307179586 * u2);
+    } else if (kind == 1) v = (double)gid[i] / 1000.0;
+    else v = cval;
+    out[i * ld + j] = (T)v;
+}
+
+// ---------------------------------------------------------------------------
+// checksum: fixed-shape two-stage sum in fp64 (bitwise reproducible).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) sum_stage1(const T* __restrict__ x, long long n, double* __restrict__ part) {
+    __shared__ double sh[256];
+    double acc = 0;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long long)gridDim.x * 256) acc += (double)x[i];
+    sh[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) { if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s]; __syncthreads(); }
+    if (threadIdx.x == 0) part[blockIdx.x] = sh[0];
+}
+__global__ void __launch_bounds__(256) sum_stage2(const double* __restrict__ part, int n, double* __restrict__ out) {
+    __shared__ double sh[256];
+    double acc = 0;
+    for (int i = threadIdx.x; i < n; i += 256) acc += part[i];
+    sh[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) { if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s]; __syncthreads(); }
+    if (threadIdx.x == 0) out[0] = sh[0];
+}
+
+// ---------------------------------------------------------------------------
+// index utilities (setup time): out[i] = table[idx[i]], inv[perm[i]] = i,
+// touch masks with atomicOr.
+// ---------------------------------------------------------------------------
+__global__ void remap_kernel(long long n, const int* __restrict__ idx, const int* __restrict__ table,
+                             long long table_len, int* __restrict__ out, int* status) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int j = idx[i];
+    if (j < 0 || j >= table_len) { report(status, ST_BAD_INDEX, 0, (int)i, j); out[i] = -1; return; }
+    out[i] = table[j];
+}
+__global__ void invert_perm_kernel(long long n, const long long* __restrict__ perm, long long* __restrict__ inv,
+                                   int* status) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long j = perm[i];
+    if (j < 0 || j >= n) { report(status, ST_BAD_INDEX, 1, (int)i, (int)j); return; }
+    inv[j] = i;
+}
+__global__ void touch_masks_kernel(long long nnz, const int* __restrict__ rows, const int* __restrict__ cols,
+                                   const int* __restrict__ rowmap, const int* __restrict__ colmap,
+                                   unsigned long long* __restrict__ row_mask, unsigned long long* __restrict__ col_mask) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nnz) return;
+    const int r = rows[i], c = cols[i];
+    atomicOr(row_mask + r, 1ull << colmap[c]);
+    atomicOr(col_mask + c, 1ull << rowmap[r]);
+}
+
+// ---- dispatch ---------------------------------------------------------------
+template <typename T>
+int launch_sddmm(long long nnz, const int* ri, const int* ci, const T* sv, const T* A, long long lda, const T* B,
+                 long long ldb, int k, T* out, cudaStream_t st) {
+    if (nnz == 0) return 0;
+    constexpr int VN = Vec<T>::N;
+    const bool vec_ok = k % VN == 0 && lda % VN == 0 && ldb % VN == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)B % 16 == 0;
+    const int nvec = k / VN;
+    if (!vec_ok || nvec > 128) {
+        long long warps = nnz < (1ll << 22) ? nnz : (1ll << 22);
+        sddmm_scalar_kernel<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(nnz, ri, ci, sv, A, lda, B, ldb, k, out);
+        return (int)cudaGetLastError();
+    }
+    const int G = pick_group(nvec);
+    const int R = (nvec + G - 1) / G;
+    const int per_slot = 16;
+    const long long slots = (nnz + per_slot - 1) / per_slot;
+    const long long warps = (slots + (32 / G) - 1) / (32 / G);
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+#define SP3_SDDMM(GG, RR) sddmm_vec_kernel<T, GG, RR><<<blocks, 256, 0, st>>>(nnz, ri, ci, sv, A, lda, B, ldb, nvec, out, per_slot)
+    if (R == 1) {
+        switch (G) {
+            case 1: SP3_SDDMM(1, 1); break;
+            case 2: SP3_SDDMM(2, 1); break;
+            case 4: SP3_SDDMM(4, 1); break;
+            case 8: SP3_SDDMM(8, 1); break;
+            case 16: SP3_SDDMM(16, 1); break;
+            default: SP3_SDDMM(32, 1); break;
+        }
+    } else if (R == 2) SP3_SDDMM(32, 2);
+    else SP3_SDDMM(32, 4);
+#undef SP3_SDDMM
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int launch_spmm(int nrows, int nitems, const int4* items, const long long* rowptr, const int* ci, const T* val,
+                const T* X, long long ldx, int k, T beta, T* Y, long long ldy, SpmmLong lg, cudaStream_t st) {
+    if (nrows == 0) return 0;
+    constexpr int VN = Vec<T>::N;
+    const bool vec_ok = k % VN == 0 && ldx % VN == 0 && ldy % VN == 0 && (uintptr_t)X % 16 == 0 &&
+                        (uintptr_t)Y % 16 == 0 && items != nullptr && (lg.ldc % VN == 0);
+    const int nvec = k / VN;
+    if (!vec_ok || nvec > 128) {
+        spmm_scalar_kernel<T><<<(unsigned)(((long long)nrows * 32 + 255) / 256), 256, 0, st>>>(nrows, rowptr, ci, val, X, ldx, k, beta, Y, ldy);
+        return (int)cudaGetLastError();
+    }
+    const int G = pick_group(nvec);
+    const int R = (nvec + G - 1) / G;
+    const unsigned blocks = (unsigned)(((long long)nitems + 7) / 8);
+#define SP3_SPMM(GG, RR) spmm_items_kernel<T, GG, RR><<<blocks, 256, 0, st>>>(nitems, items, rowptr, ci, val, X, ldx, nvec, beta, Y, ldy, lg)
+    if (R == 1) {
+        switch (G) {
+            case 1: SP3_SPMM(1, 1); break;
+            case 2: SP3_SPMM(2, 1); break;
+            case 4: SP3_SPMM(4, 1); break;
+            case 8: SP3_SPMM(8, 1); break;
+            case 16: SP3_SPMM(16, 1); break;
+            default: SP3_SPMM(32, 1); break;
+        }
+    } else if (R == 2) SP3_SPMM(32, 2);
+    else SP3_SPMM(32, 4);
+#undef SP3_SPMM
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int launch_rows(int mode, long long n, const long long* idx, const T* src, long long lds, T* dst, long long ldd, int k,
+                cudaStream_t st) {
+    if (n == 0) return 0;
+    constexpr int VN = Vec<T>::N;
+    const bool vec_ok = k % VN == 0 && lds % VN == 0 && ldd % VN == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)dst % 16 == 0;
+    const int nvec = vec_ok ? k / VN : k;
+    const int per_warp = 32 / pick_group(nvec);
+    const long long warps = (n + per_warp - 1) / per_warp;
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    if (vec_ok) rows_kernel<T, true><<<blocks, 256, 0, st>>>(mode, n, idx, src, lds, dst, ldd, k);
+    else rows_kernel<T, false><<<blocks, 256, 0, st>>>(mode, n, idx, src, lds, dst, ldd, k);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace sp3
+
+using namespace sp3;
+
+SP3_API int sp3_cuda_sddmm_f32(long long nnz, const int* ri, const int* ci, const float* sv, const float* A,
+                               long long lda, const float* B, long long ldb, int k, float* out, void* stream) {
+    return launch_sddmm<float>(nnz, ri, ci, sv, A, lda, B, ldb, k, out, (cudaStream_t)stream);
+}
+SP3_API int sp3_cuda_sddmm_f64(long long nnz, const int* ri, const int* ci, const double* sv, const double* A,
+                               long long lda, const double* B, long long ldb, int k, double* out, void* stream) {
+    return launch_sddmm<double>(nnz, ri, ci, sv, A, lda, B, ldb, k, out, (cudaStream_t)stream);
+}
+
+// items may be null (then the unscheduled one-warp-per-row kernel runs).
+// Long-row arguments may be null/0 when the schedule has no long rows.
+SP3_API int sp3_cuda_spmm_f32(int nrows, int nitems, const void* items, const long long* rowptr, const int* ci,
+                              const float* val, const float* X, long long ldx, int k, float beta, float* Y,
+                              long long ldy, const int* first_piece, const int* npieces, int* counters,
+                              void* carry, long long ldc, int piece_len, void* stream) {
+    SpmmLong lg{first_piece, npieces, counters, carry, ldc, piece_len};
+    return launch_spmm<float>(nrows, nitems, (const int4*)items, rowptr, ci, val, X, ldx, k, beta, Y, ldy, lg,
+                              (cudaStream_t)stream);
+}
+SP3_API int sp3_cuda_spmm_f64(int nrows, int nitems, const void* items, const long long* rowptr, const int* ci,
+                              const double* val, const double* X, long long ldx, int k, double beta, double* Y,
+                              long long ldy, const int* first_piece, const int* npieces, int* counters,
+                              void* carry, long long ldc, int piece_len, void* stream) {
+    SpmmLong lg{first_piece, npieces, counters, carry, ldc, piece_len};
+    return launch_spmm<double>(nrows, nitems, (const int4*)items, rowptr, ci, val, X, ldx, k, beta, Y, ldy, lg,
+                               (cudaStream_t)stream);
+}
+SP3_API int sp3_cuda_rows_f32(int mode, long long n, const long long* idx, const float* src, long long lds,
+                              float* dst, long long ldd, int k, void* stream) {
+    return launch_rows<float>(mode, n, idx, src, lds, dst, ldd, k, (cudaStream_t)stream);
+}
+SP3_API int sp3_cuda_rows_f64(int mode, long long n, const long long* idx, const double* src, long long lds,
+                              double* dst, long long ldd, int k, void* stream) {
+    return launch_rows<double>(mode, n, idx, src, lds, dst, ldd, k, (cudaStream_t)stream);
+}
+SP3_API int sp3_cuda_fill_rows_f32(const long long* gid, long long nrows, long long col0, int ncols, long long ld,
+                                   long long kglobal, int kind, double cval, unsigned long long seed,
+                                   unsigned long long stream_id, float* out, void* stream) {
+    const long long n = nrows * ncols;
+    if (n == 0) return 0;
+    fill_rows_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gid, nrows, col0, ncols, ld, kglobal, kind, cval, seed, stream_id, out);
+    return (int)cudaGetLastError();
+}
+SP3_API int sp3_cuda_fill_rows_f64(const long long* gid, long long nrows, long long col0, int ncols, long long ld,
+                                   long long kglobal, int kind, double cval, unsigned long long seed,
+                                   unsigned long long stream_id, double* out, void* stream) {
+    const long long n = nrows * ncols;
+    if (n == 0) return 0;
+    fill_rows_kernel<double><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gid, nrows, col0, ncols, ld, kglobal, kind, cval, seed, stream_id, out);
+    return (int)cudaGetLastError();
+}
+// part must hold 1024 doubles of scratch; out one double.
+SP3_API int sp3_cuda_sum_f32(const float* x, long long n, double* part, double* out, void* stream) {
+    sum_stage1<float><<<1024, 256, 0, (cudaStream_t)stream>>>(x, n, part);
+    sum_stage2<<<1, 256, 0, (cudaStream_t)stream>>>(part, 1024, out);
+    return (int)cudaGetLastError();
+}
+SP3_API int sp3_cuda_sum_f64(const double* x, long long n, double* part, double* out, void* stream) {
+    sum_stage1<double><<<1024, 256, 0, (cudaStream_t)stream>>>(x, n, part);
+    sum_stage2<<<1, 256, 0, (cudaStream_t)stream>>>(part, 1024, out);
+    return (int)cudaGetLastError();
+}
+SP3_API int sp3_cuda_remap(long long n, const int* idx, const int* table, long long table_len, int* out,
+                           int* status, void* stream) {
+    if (n == 0) return 0;
+    remap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, idx, table, table_len, out, status);
+    return (int)cudaGetLastError();
+}
+SP3_API int sp3_cuda_invert_perm(long long n, const long long* perm, long long* inv, int* status, void* stream) {
+    if (n == 0) return 0;
+    invert_perm_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, perm, inv, status);
+    return (int)cudaGetLastError();
+}
+SP3_API int sp3_cuda_touch_masks(long long nnz, const int* rows, const int* cols, const int* rowmap,
+                                 const int* colmap, void* row_mask, void* col_mask, void* stream) {
+    if (nnz == 0) return 0;
+    touch_masks_kernel<<<(unsigned)((nnz + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        nnz, rows, cols, rowmap, colmap, (unsigned long long*)row_mask, (unsigned long long*)col_mask);
+    return (int)cudaGetLastError();
+}

@@ -97,10 +97,21 @@ class _Dist3DOp:
             buf[side.n_owned:].fill_(float("nan"))
 
     def _finish(self):
+        if not self.timer.enabled:
+            return None
         self.last_times = self.timer.collect()
         t = self.last_times
         t["total"] = t.get("comm1", 0.0) + t.get("comp", 0.0) + t.get("comm2", 0.0)
         return t
+
+    def run_async(self, *a, **kw):
+        """`run` without phase timers: no host synchronisation, for callers
+        that time a whole loop themselves."""
+        self.timer.enabled = False
+        try:
+            return self.run(*a, **kw)
+        finally:
+            self.timer.enabled = True
 
     def alg_name(self, phase: str) -> str:
         return f"{ALG_NAMES[self.variant]} {self.kernel} {phase}"

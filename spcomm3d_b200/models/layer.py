@@ -1,0 +1,124 @@
+"""Pipelines built from the two distributed kernels.
+
+`SddmmSpmmStep`  one SDDMM followed by one SpMM on the same sparse matrix with
+                 its stored values: the unit the benchmarks time (the
+                 reference runs the two kernels as separate programs,
+                 miniapp/bench_both.cpp and miniapp/bench_spmm.cpp, or back to
+                 back in miniapp/main_combined.cpp:165-281).
+`GatLayer`       attention-style chain: edge scores C = S o (A B^T), then
+                 Y = C X with the scores as the sparse values.  The scores are
+                 summed along the Z fiber and then shared by the whole fiber,
+                 because every Z layer multiplies the full block with its own
+                 slice of X's columns.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.mesh import split_nnz
+from .dist_ops import DistSDDMM, DistSpMM
+
+STREAM_A, STREAM_B = 1, 2
+
+
+class SddmmSpmmStep:
+    def __init__(self, plan, groups, k, dtype=torch.float32, device="cuda", variant="sparseNRB", seed=0):
+        self.plan, self.k, self.seed = plan, k, seed
+        self.device = torch.device(device)
+        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant)
+        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant)
+        self.host = None
+
+    def fill_device_operands(self):
+        """A, B (and X = B) generated on the device from the seed."""
+        sd, sp, p = self.sddmm, self.spmm, self.plan
+        if self.device.type == "cuda":
+            from ..ops import cuda_ops
+            ga = torch.from_numpy(p.row.owned_gids).to(self.device)
+            gb = torch.from_numpy(p.col.owned_gids).to(self.device)
+            cuda_ops.fill_rows(ga, self.k, sd.k_off, sd.A_owned, seed=self.seed, stream=STREAM_A)
+            cuda_ops.fill_rows(gb, self.k, sd.k_off, sd.B_owned, seed=self.seed, stream=STREAM_B)
+            sp.X_owned.copy_(sd.B_owned)
+        else:
+            sd.fill_owned(sd.A_owned, p.row.owned_gids, seed=self.seed, stream=STREAM_A)
+            sd.fill_owned(sd.B_owned, p.col.owned_gids, seed=self.seed, stream=STREAM_B)
+            sp.X_owned.copy_(sd.B_owned)
+
+    def run_device(self):
+        c = self.sddmm.run_async()
+        y = self.spmm.run_async()
+        return c, y
+
+    # ---- end to end: operands start in pinned host memory -----------------
+    def make_host_operands(self):
+        sd = self.sddmm
+        pin = self.device.type == "cuda"
+        self.host = {"A": sd.A_owned.cpu(), "B": sd.B_owned.cpu()}
+        if pin:
+            self.host = {n: t.pin_memory() for n, t in self.host.items()}
+        self._sums = torch.zeros(2, dtype=torch.float64, device=self.device)
+        return self.host
+
+    @property
+    def h2d_bytes(self):
+        h = self.host
+        return int(h["A"].numel() * h["A"].element_size() + 2 * h["B"].numel() * h["B"].element_size())
+
+    @property
+    def d2h_bytes(self):
+        return 16
+
+    def run_e2e(self):
+        """Copies A, B and X from host memory, runs SDDMM then SpMM and reads
+        back the checksums of this rank's results (two fp64 scalars)."""
+        sd, sp, h = self.sddmm, self.spmm, self.host
+        sd.A_owned.copy_(h["A"], non_blocking=True)
+        sd.B_owned.copy_(h["B"], non_blocking=True)
+        sp.X_owned.copy_(h["B"], non_blocking=True)
+        c = sd.run_async()
+        y = sp.run_async()
+        if self.device.type == "cuda":
+            from ..ops import cuda_ops
+            self._sums[0:1].copy_(cuda_ops.checksum(c))
+            self._sums[1:2].copy_(cuda_ops.checksum(y.reshape(-1)))
+        else:
+            self._sums[0], self._sums[1] = c.double().sum(), y.double().sum()
+        return self._sums.cpu().tolist()
+
+    def comm_volume_bytes(self):
+        """[sddmm expand, sddmm z-reduce, spmm expand, spmm reduce] bytes this
+        rank receives per step according to the plan."""
+        es = self.sddmm.A_loc.element_size()
+        pre, post = (self.sddmm.comm_stats()[p] for p in ("PRE", "POST"))
+        z = self.plan.mesh.Z
+        zred = (self.plan.nnz - post[1][1]) if z > 1 else 0  # values leaving this rank
+        spre, spost = (self.spmm.comm_stats()[p] for p in ("PRE", "POST"))
+        return [pre[1][1] * es, zred * es, spre[1][1] * es, spost[1][1] * es]
+
+
+class GatLayer:
+    """Y = (S o (A B^T)) X on the mesh; returns owned rows of Y."""
+
+    def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB"):
+        self.plan, self.groups = plan, groups
+        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant)
+        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant)
+        Z = plan.mesh.Z
+        self.slices = [split_nnz(plan.nnz, Z, z) for z in range(Z)]
+        self.width = self.slices[0][1]
+        dev = torch.device(device)
+        self._mine = torch.zeros(self.width, dtype=dtype, device=dev)
+        self._all = torch.zeros(Z, self.width, dtype=dtype, device=dev)
+
+    def run(self):
+        c = self.sddmm.run()
+        Z = self.plan.mesh.Z
+        if Z == 1:
+            self.spmm.vals.copy_(c)
+        else:
+            self._mine[:c.shape[0]].copy_(c)
+            dist.all_gather_into_tensor(self._all.view(-1), self._mine, group=self.groups.fiber)
+            for z, (o, l) in enumerate(self.slices):
+                self.spmm.vals[o:o + l].copy_(self._all[z, :l])
+        return self.spmm.run()

@@ -1,0 +1,173 @@
+"""Python front end of the local sm_100a kernels (csrc/kernels/local_ops.cu).
+
+Every function launches on the current torch CUDA stream and passes raw device
+pointers; nothing here falls back to a torch implementation.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..utils import native
+
+_F = {torch.float32: "f32", torch.float64: "f64"}
+
+# SpMM schedule parameters: rows with more than LONG_ROW nonzeros are cut into
+# pieces of LONG_ROW; other rows are grouped into items of about ITEM_NNZ
+# nonzeros and at most ITEM_ROWS rows.
+LONG_ROW = 512
+ITEM_NNZ = 128
+ITEM_ROWS = 64
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+LAUNCHES = 0  # kernels launched through this module (bench.py reports the count)
+
+
+def _ck(rc, what, n=1):
+    global LAUNCHES
+    LAUNCHES += n
+    if rc != 0:
+        raise RuntimeError(f"{what}: CUDA launch error {rc}")
+
+
+def _ld(t):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("dense operand must be 2-D with unit inner stride")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def sddmm(rowidx, colidx, svals, A, B, out):
+    fn = getattr(native.cuda(), f"sp3_cuda_sddmm_{_F[A.dtype]}")
+    _ck(fn(rowidx.shape[0], native.ptr(rowidx), native.ptr(colidx), native.ptr(svals), native.ptr(A), _ld(A),
+           native.ptr(B), _ld(B), A.shape[1], native.ptr(out), _stream()), "sddmm")
+    return out
+
+
+def build_spmm_items(rowptr: np.ndarray, long_row: int = LONG_ROW, item_nnz: int = ITEM_NNZ,
+                     item_rows: int = ITEM_ROWS):
+    """Work items of the SpMM kernel from a CSR row pointer (host, vectorised).
+
+    Returns (items int32[n,4], first_piece int32[nlong], npieces int32[nlong]).
+    rows item  = (row_begin, row_end, 0, -1)
+    piece item = (row, nnz_begin, nnz_end, long_row_slot)
+    """
+    nrows = rowptr.shape[0] - 1
+    deg = np.diff(rowptr)
+    is_long = deg > long_row
+    key = rowptr[:-1] // item_nnz
+    bnd = np.ones(nrows, bool)
+    if nrows > 1:
+        bnd[1:] = (key[1:] != key[:-1]) | (np.arange(1, nrows) % item_rows == 0) | is_long[1:] | is_long[:-1]
+    starts = np.flatnonzero(bnd)
+    ends = np.append(starts[1:], nrows)
+    short = ~is_long[starts]
+    rows_items = np.stack([starts[short], ends[short], np.zeros(short.sum(), np.int64),
+                           -np.ones(short.sum(), np.int64)], axis=1)
+    long_rows = np.flatnonzero(is_long)
+    npieces = (deg[long_rows] + long_row - 1) // long_row
+    first = np.concatenate([[0], np.cumsum(npieces)[:-1]]) if long_rows.size else np.zeros(0, np.int64)
+    if long_rows.size:
+        slot = np.repeat(np.arange(long_rows.size), npieces)
+        j = np.arange(int(npieces.sum())) - np.repeat(first, npieces)
+        r = long_rows[slot]
+        b = rowptr[r] + j * long_row
+        e = np.minimum(b + long_row, rowptr[r + 1])
+        piece_items = np.stack([r, b, e, slot], axis=1)
+        items = np.concatenate([piece_items, rows_items])  # heavy work first
+    else:
+        items = rows_items
+    if items.size and items.max() >= 2 ** 31:
+        raise ValueError("more than 2^31 nonzeros or rows on one rank")
+    return items.astype(np.int32), first.astype(np.int32), npieces.astype(np.int32)
+
+
+class SpmmSchedule:
+    """Device-resident SpMM work items plus the scratch the long-row path
+    needs: one carry row per piece and one counter per long row."""
+
+    def __init__(self, rowptr: torch.Tensor, k_max: int = 0, dtype=torch.float32, **kw):
+        rp = rowptr.cpu().numpy()
+        items, first, npieces = build_spmm_items(rp, **kw)
+        dev = rowptr.device
+        self.piece_len = kw.get("long_row", LONG_ROW)
+        self.items = torch.from_numpy(items).to(dev).contiguous()
+        self.first = torch.from_numpy(first).to(dev)
+        self.npieces = torch.from_numpy(npieces).to(dev)
+        self.counters = torch.zeros(max(1, first.shape[0]), dtype=torch.int32, device=dev)
+        self.total_pieces = int(npieces.sum())
+        self.carry = None
+        self.nlong = int(first.shape[0])
+
+    def carry_for(self, k: int, dtype, device):
+        if self.total_pieces == 0:
+            return None, 0
+        if self.carry is None or self.carry.shape[1] < k or self.carry.dtype != dtype:
+            self.carry = torch.empty(self.total_pieces, k, dtype=dtype, device=device)
+        return self.carry, self.carry.stride(0)
+
+
+def spmm(rowptr, rowidx, colidx, vals, X, Y, beta, sched: SpmmSchedule | None):
+    if sched is None:
+        sched = SpmmSchedule(rowptr)
+    carry, ldc = sched.carry_for(X.shape[1], X.dtype, X.device)
+    fn = getattr(native.cuda(), f"sp3_cuda_spmm_{_F[X.dtype]}")
+    _ck(fn(rowptr.shape[0] - 1, sched.items.shape[0], native.ptr(sched.items), native.ptr(rowptr),
+           native.ptr(colidx), native.ptr(vals), native.ptr(X), _ld(X), X.shape[1], float(beta), native.ptr(Y),
+           _ld(Y), native.ptr(sched.first), native.ptr(sched.npieces), native.ptr(sched.counters),
+           native.ptr(carry), ldc, sched.piece_len, _stream()), "spmm")
+    return Y
+
+
+def rows(mode, idx, src, dst):
+    fn = getattr(native.cuda(), f"sp3_cuda_rows_{_F[src.dtype]}")
+    _ck(fn(mode, idx.shape[0], native.ptr(idx), native.ptr(src), _ld(src), native.ptr(dst), _ld(dst),
+           src.shape[1], _stream()), "rows")
+    return dst
+
+
+def fill_rows(gids: torch.Tensor, k_global, col0, out: torch.Tensor, *, kind=0, const=0.0, seed=0, stream=0):
+    """Device twin of utils.generate.fill_rows: writes into out[len(gids), ncols]."""
+    fn = getattr(native.cuda(), f"sp3_cuda_fill_rows_{_F[out.dtype]}")
+    _ck(fn(native.ptr(gids), gids.shape[0], col0, out.shape[1], _ld(out), k_global, kind, float(const), seed,
+           stream, native.ptr(out), _stream()), "fill_rows")
+    return out
+
+
+def checksum(x: torch.Tensor) -> torch.Tensor:
+    """fp64 sum of a 1-D fp32/fp64 tensor with a fixed reduction shape."""
+    part = torch.empty(1024, dtype=torch.float64, device=x.device)
+    out = torch.empty(1, dtype=torch.float64, device=x.device)
+    fn = getattr(native.cuda(), f"sp3_cuda_sum_{_F[x.dtype]}")
+    _ck(fn(native.ptr(x), x.numel(), native.ptr(part), native.ptr(out), _stream()), "checksum", 2)
+    return out
+
+
+def new_status(device):
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def remap_indices(idx: torch.Tensor, table: torch.Tensor, status=None) -> torch.Tensor:
+    out = torch.empty_like(idx)
+    st = new_status(idx.device) if status is None else status
+    _ck(native.cuda().sp3_cuda_remap(idx.shape[0], native.ptr(idx), native.ptr(table), table.shape[0],
+                                     native.ptr(out), native.ptr(st), _stream()), "remap")
+    return out
+
+
+def invert_perm(perm: torch.Tensor, status=None) -> torch.Tensor:
+    inv = torch.empty_like(perm)
+    st = new_status(perm.device) if status is None else status
+    _ck(native.cuda().sp3_cuda_invert_perm(perm.shape[0], native.ptr(perm), native.ptr(inv), native.ptr(st),
+                                           _stream()), "invert_perm")
+    return inv
+
+
+def touch_masks(rows_, cols_, rowmap, colmap, row_mask, col_mask):
+    _ck(native.cuda().sp3_cuda_touch_masks(rows_.shape[0], native.ptr(rows_), native.ptr(cols_),
+                                           native.ptr(rowmap), native.ptr(colmap), native.ptr(row_mask),
+                                           native.ptr(col_mask), _stream()), "touch_masks")
+    return row_mask, col_mask

@@ -45,6 +45,7 @@ class PhaseTimer:
         self.cuda = torch.device(device).type == "cuda"
         self.ms: dict[str, float] = {}
         self._pending = []
+        self.enabled = True
 
     class _Span:
         def __init__(self, timer, name):
@@ -68,7 +69,7 @@ class PhaseTimer:
             return False
 
     def span(self, name):
-        return PhaseTimer._Span(self, name)
+        return PhaseTimer._Span(self, name) if self.enabled else _NullSpan()
 
     def collect(self) -> dict:
         """Synchronises (GPU) and returns {phase: ms}, then resets."""

@@ -126,7 +126,7 @@ def host_build_cmd():
 def cuda_build_cmd(verbose_ptxas=False):
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", *NVCC_ARCH, "-shared", "-Xcompiler", "-fPIC",
-           "-Xcompiler", "-fvisibility=hidden", f"-I{CSRC / 'kernels'}", "-lcuda"]
+           "-Xcompiler", "-fvisibility=hidden", f"-I{CSRC / 'kernels'}"]
     if verbose_ptxas:
         cmd += ["-Xptxas", "-v"]
     return cmd
