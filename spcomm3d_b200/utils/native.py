@@ -89,7 +89,9 @@ def _stamp(files, flags) -> str:
     for f in files:
         h.update(f.name.encode())
         h.update(f.read_bytes())
-    h.update(" ".join(flags).encode())
+    # flags enter the stamp with the checkout path removed, so a snapshot of
+    # the tree copied elsewhere does not look stale
+    h.update(" ".join(flags).replace(str(REPO), ".").encode())
     return h.hexdigest()
 
 
