@@ -529,3 +529,59 @@ SP3_API int sp3_cuda_touch_masks(long long nnz, const int* rows, const int* cols
         nnz, rows, cols, rowmap, colmap, (unsigned long long*)row_mask, (unsigned long long*)col_mask);
     return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// SpMM entry point that allocates nothing (declared in sp3_noalloc.h).
+//
+// The scheduled SpMM kernel needs scratch for rows that are split into
+// pieces: one partial row per piece plus one arrival counter per split row.
+// Callers that are not allowed to call cudaMalloc (see the header) get that
+// scratch from the fixed array below instead of from an allocation.  The
+// array is part of the loaded library image: every GPU that loads the library
+// holds SP3_NOALLOC_SCRATCH_BYTES of device memory until the process exits.
+// ---------------------------------------------------------------------------
+#include "sp3_noalloc.h"
+
+namespace {
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SP3_NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// Device address of g_noalloc_scratch per device ordinal, filled on the first
+// call made with that device current.  In host code the symbol name itself is
+// only a handle; the address has to come from cudaGetSymbolAddress.
+unsigned char* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace
+
+SP3_API int sp3_cuda_spmm_f32_noalloc(int nrows, int nitems, const void* items, const long long* rowptr,
+                                      const int* colidx, const float* val, const float* X, long long ldx, int k,
+                                      float beta, float* Y, long long ldy, const int* first_piece,
+                                      const int* npieces, int nlong, int total_pieces, int piece_len,
+                                      void* stream) {
+    if (nrows < 0 || nitems < 0 || nlong < 0 || total_pieces < 0 || k <= 0) return SP3_NOALLOC_E_ARG;
+    // layout of the scratch: [counters: SP3_NOALLOC_MAX_SPLIT_ROWS x int32][carry: total_pieces x ldc floats]
+    const long long ldc = ((long long)k + 3) / 4 * 4;  // keep carry rows 16-byte aligned
+    const size_t counters_bytes = (size_t)SP3_NOALLOC_MAX_SPLIT_ROWS * sizeof(int);
+    const size_t carry_bytes = (size_t)total_pieces * (size_t)ldc * sizeof(float);
+    if (nlong > SP3_NOALLOC_MAX_SPLIT_ROWS || counters_bytes + carry_bytes > (size_t)SP3_NOALLOC_SCRATCH_BYTES)
+        return SP3_NOALLOC_E_TOO_LARGE;
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return (int)err;
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SP3_NOALLOC_E_ARG;
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (err != cudaSuccess) return (int)err;
+        g_noalloc_ptr[dev] = (unsigned char*)p;
+    }
+    unsigned char* base = g_noalloc_ptr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+    if (nlong > 0) {
+        // the array keeps whatever the previous call left; counters must start at zero
+        err = cudaMemsetAsync(base, 0, (size_t)nlong * sizeof(int), st);
+        if (err != cudaSuccess) return (int)err;
+    }
+    sp3::SpmmLong lg{first_piece, npieces, (int*)base, (void*)(base + counters_bytes), ldc, piece_len};
+    return sp3::launch_spmm<float>(nrows, nitems, (const int4*)items, rowptr, colidx, val, X, ldx, k, beta, Y, ldy,
+                                   lg, st);
+}
