@@ -5,6 +5,8 @@ pointers; nothing here falls back to a torch implementation.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -15,9 +17,9 @@ _F = {torch.float32: "f32", torch.float64: "f64"}
 # SpMM schedule parameters: rows with more than LONG_ROW nonzeros are cut into
 # pieces of LONG_ROW; other rows are grouped into items of about ITEM_NNZ
 # nonzeros and at most ITEM_ROWS rows.
-LONG_ROW = 512
-ITEM_NNZ = 128
-ITEM_ROWS = 64
+LONG_ROW = int(os.environ.get("SP3_LONG_ROW", 512))
+ITEM_NNZ = int(os.environ.get("SP3_ITEM_NNZ", 128))
+ITEM_ROWS = int(os.environ.get("SP3_ITEM_ROWS", 64))
 
 
 def _stream():
@@ -47,14 +49,17 @@ def sddmm(rowidx, colidx, svals, A, B, out):
     return out
 
 
-def build_spmm_items(rowptr: np.ndarray, long_row: int = LONG_ROW, item_nnz: int = ITEM_NNZ,
-                     item_rows: int = ITEM_ROWS):
+def build_spmm_items(rowptr: np.ndarray, long_row: int | None = None, item_nnz: int | None = None,
+                     item_rows: int | None = None):
     """Work items of the SpMM kernel from a CSR row pointer (host, vectorised).
 
     Returns (items int32[n,4], first_piece int32[nlong], npieces int32[nlong]).
     rows item  = (row_begin, row_end, 0, -1)
     piece item = (row, nnz_begin, nnz_end, long_row_slot)
     """
+    long_row = LONG_ROW if long_row is None else long_row
+    item_nnz = ITEM_NNZ if item_nnz is None else item_nnz
+    item_rows = ITEM_ROWS if item_rows is None else item_rows
     nrows = rowptr.shape[0] - 1
     deg = np.diff(rowptr)
     is_long = deg > long_row
