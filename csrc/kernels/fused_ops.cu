@@ -1,0 +1,440 @@
+// Fused compute + communication kernels for sm_100a (fp32).
+//
+// One persistent kernel per distributed op.  Instead of "pack, message, unpack,
+// compute, message, add" (the reference's phased pipelines,
+// src/distributed_comp.cpp:17-76 for SpMM and :141-284 for SDDMM, with the
+// staging copies of src/comm.hpp:90-103,166-189), every rank's kernel
+//
+//   * pulls the dense rows it needs on the column side (B for SDDMM, X for
+//     SpMM) straight out of the owners' memory over NVLink into its local
+//     block, tile by tile, while other warps already compute;
+//   * reads the row-side operand of SDDMM (A rows) directly from the owner's
+//     memory -- each such row is consumed by one work unit, so it crosses
+//     NVLink exactly once and is never staged;
+//   * SDDMM: stores every partial dot product directly into the value buffer
+//     of the fiber rank that owns that nonzero after the Z reduction, and then
+//     sums the Z partial vectors of its own slice (the reduce-scatter of
+//     src/denseComm.hpp:35-40 becomes remote stores + a local sum);
+//   * SpMM: stores finished partial rows of rows it does not own directly into
+//     a slot in the owner's memory; the owner adds its own partial and the
+//     slots in ascending source order (bitwise reproducible), which is the
+//     role-swapped exchange + SUM_from_recvbuff of src/comm.hpp:178-189.
+//
+// Moved data is exactly what the plan lists (the sparsity-aware minimum).
+//
+// Cross-GPU ordering uses three flags per (source rank, kind) in a signal pad
+// in every rank's symmetric heap, written with st.release.sys and read with
+// ld.acquire.sys, carrying the epoch (launch number) of the op:
+//   READY  "my operands for this epoch may be read"      -> my readers
+//   DONE   "I no longer read your memory this epoch"      -> ranks I read from
+//   PART   "my partial results for this epoch are in your memory" -> targets
+// A kernel returns only after every rank that reads its memory has signalled
+// DONE, so when the op completes the caller may overwrite its operands.
+// Partial-result buffers are double buffered by epoch parity.  Every wait is
+// bounded: on timeout the kernel records {code, site, peer, value} in the
+// status words, raises the abort flag so the other warps drain, and returns.
+//
+// The three phases (START = publish READY, MAIN = pull + compute + push,
+// FINISH = reduce + final handshake) run in one launch; they can also be
+// launched one at a time, which lets a single GPU run all ranks of a mesh in
+// lock step (each phase of every rank before the next phase) without any
+// kernel ever waiting on a later launch.
+#include "sp3_kernels.cuh"
+
+namespace sp3 {
+
+constexpr int MAX_RANKS = 64;
+enum FlagKind : int { F_READY = 0, F_DONE = 1, F_PART = 2, F_KINDS = 3 };
+enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_WORDS = 8 };
+enum Phase : int { PH_START = 1, PH_MAIN = 2, PH_FINISH = 4 };
+enum WaitSite : int { W_READY = 1, W_PULLS = 2, W_PART = 3, W_DONE = 4 };
+
+constexpr int PULL_ROWS = 64;      // dense rows per pull ticket
+constexpr int REDUCE_ELEMS = 2048; // values per SDDMM reduce ticket
+constexpr int REDUCE_ROWS = 32;    // owned rows per SpMM reduce ticket
+
+struct FusedComm {
+    int me;                  // my world rank
+    int epoch;               // launch number of this op, >= 1
+    int phases;              // Phase bits
+    unsigned long long timeout_ns;
+    int* status;             // int[4] local
+    int* ctrl;               // int[C_WORDS] local, zero at launch
+    int* pad;                // my signal pad, int[F_KINDS][MAX_RANKS], indexed by source rank
+    int* const* peer_pad;    // [world] every rank's pad as mapped into this process
+    const int* read_from;    // ranks whose memory I read
+    const int* readers;      // ranks that read my memory
+    const int* push_to;      // ranks I push partial results to
+    const int* contrib;      // ranks that push partial results to me
+    int n_read, n_readers, n_push, n_contrib;
+};
+
+__device__ __forceinline__ int warp_ticket(int* ctr, int lane) {
+    int t = 0;
+    if (lane == 0) t = atomicAdd(ctr, 1);
+    return __shfl_sync(0xffffffffu, t, 0);
+}
+
+__device__ __forceinline__ bool aborted(const FusedComm& c) {
+    return *reinterpret_cast<volatile int*>(c.ctrl + C_ABORT) != 0;
+}
+
+__device__ __forceinline__ void signal(const FusedComm& c, int kind, int dst) {
+    st_release_sys(c.peer_pad[dst] + kind * MAX_RANKS + c.me, c.epoch);
+}
+
+// Bounded wait for flag[kind][src] >= epoch.  All lanes may call it; they all
+// poll (reads of one word).  On timeout: status record + abort flag.
+__device__ __forceinline__ bool wait_flag(const FusedComm& c, int kind, int src, int site) {
+    const int* f = c.pad + kind * MAX_RANKS + src;
+    if (ld_acquire_sys(f) >= c.epoch) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 32; ++i) {
+            if (ld_acquire_sys(f) >= c.epoch) return true;
+            __nanosleep(100);
+        }
+        if (aborted(c)) return false;
+        if (globaltimer_ns() - t0 > c.timeout_ns) {
+            report(c.status, ST_WAIT_TIMEOUT, site, src, ld_acquire_sys(f));
+            atomicExch(c.ctrl + C_ABORT, 1);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ bool wait_all(const FusedComm& c, int kind, const int* list, int n, int site) {
+    bool ok = true;
+    for (int i = 0; i < n; ++i) ok = wait_flag(c, kind, list[i], site) && ok;
+    return ok;
+}
+
+__device__ __forceinline__ bool wait_counter(const FusedComm& c, int which, int want, int site) {
+    const int* p = c.ctrl + which;
+    if (ld_acquire_gpu(p) >= want) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 32; ++i) {
+            if (ld_acquire_gpu(p) >= want) return true;
+            __nanosleep(64);
+        }
+        if (aborted(c)) return false;
+        if (globaltimer_ns() - t0 > c.timeout_ns) {
+            report(c.status, ST_WAIT_TIMEOUT, site, which, ld_acquire_gpu(p));
+            atomicExch(c.ctrl + C_ABORT, 1);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void start_phase(const FusedComm& c) {
+    if (blockIdx.x == 0 && threadIdx.x < c.n_readers) {
+        __threadfence_system();
+        signal(c, F_READY, c.readers[threadIdx.x]);
+    }
+}
+
+// Copies dense rows [r0, r1) of a receive list from their owners' memory
+// (src[r] = absolute address of the row, local or peer) into the local block.
+// The tile is treated as a flat list of 16-byte vectors, four per lane in
+// flight, so a warp keeps 2 KB of NVLink reads outstanding.
+__device__ __forceinline__ void pull_rows(int r0, int r1, const float4* const* __restrict__ src,
+                                          float4* __restrict__ dst, long long ld_v, int nvec, int lane) {
+    const int total = (r1 - r0) * nvec;
+    for (int base = 0; base < total; base += 128) {
+        float4 v[4];
+        int row[4], vec[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = base + u * 32 + lane;
+            row[u] = e < total ? e / nvec : -1;
+            vec[u] = e - row[u] * nvec;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (row[u] >= 0) v[u] = __ldcs(ldg_ptr(src + r0 + row[u]) + vec[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (row[u] >= 0) dst[(long long)(r0 + row[u]) * ld_v + vec[u]] = v[u];
+    }
+}
+
+// Every warp calls this after its MAIN work; the last one to arrive publishes
+// DONE and PART for this rank.
+__device__ __forceinline__ void main_epilogue(const FusedComm& c, int lane, int nwarps) {
+    __threadfence_system();
+    __syncwarp();
+    int old = 0;
+    if (lane == 0) old = atomicAdd(c.ctrl + C_MAIN_DONE, 1);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old == nwarps - 1) {
+        __threadfence_system();
+        for (int i = lane; i < c.n_read; i += 32) signal(c, F_DONE, c.read_from[i]);
+        for (int i = lane; i < c.n_push; i += 32) signal(c, F_PART, c.push_to[i]);
+    }
+}
+
+// Last warp of the FINISH phase keeps the kernel alive until every reader of
+// this rank's memory is done with it.
+__device__ __forceinline__ void finish_epilogue(const FusedComm& c, int lane, int nwarps) {
+    __syncwarp();
+    int old = 0;
+    if (lane == 0) old = atomicAdd(c.ctrl + C_FIN_DONE, 1);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old == nwarps - 1 && lane == 0) wait_all(c, F_DONE, c.readers, c.n_readers, W_DONE);
+}
+
+// ---------------------------------------------------------------------------
+// SDDMM
+// ---------------------------------------------------------------------------
+struct FusedSddmmArgs {
+    FusedComm comm;
+    long long nnz;
+    const int* rowidx;
+    const int* colidx;
+    const float* sval;
+    const float4* const* a_rows;  // [rows of the local A layout] absolute row addresses
+    float* B_loc;                 // local B block [owned | pulled]
+    long long ldb;
+    int n_owned_b, n_recv_b;
+    const float4* const* b_src;   // [n_recv_b] absolute addresses of the rows to pull
+    int nvec;
+    int Z, my_z;
+    unsigned zbase, zrem;         // slice lengths: zbase (+1 for the first zrem fiber ranks)
+    long long zwidth;             // elements reserved per (parity, source) in a value buffer
+    float* const* zbuf;           // [Z] value buffers of the fiber ranks (mine is local)
+    float* out;                   // my slice of C
+};
+
+struct StoreSlices {
+    const float* sval;
+    float* out;
+    float* const* zbuf;
+    int Z, my_z, parity;
+    unsigned zbase, zrem;
+    long long zwidth;
+    __device__ __forceinline__ void operator()(long long i, float dot) const {
+        const float v = dot * __ldg(sval + i);
+        if (Z == 1) { out[i] = v; return; }
+        const unsigned ii = (unsigned)i, split = zrem * (zbase + 1);
+        unsigned zo, off;
+        if (ii < split) { zo = ii / (zbase + 1); off = zo * (zbase + 1); }
+        else { zo = zrem + (ii - split) / zbase; off = split + (zo - zrem) * zbase; }
+        zbuf[zo][((long long)parity * Z + my_z) * zwidth + (ii - off)] = v;
+    }
+};
+
+template <int G, int R, int U>
+__global__ void __launch_bounds__(256) fused_sddmm_kernel(const FusedSddmmArgs a) {
+    const FusedComm& c = a.comm;
+    const int lane = threadIdx.x & 31;
+    const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
+    const int parity = c.epoch & 1;
+    if (c.phases & PH_START) start_phase(c);
+    if (c.phases & PH_MAIN) {
+        bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
+        constexpr int SLOTS = 32 / G;
+        const int n_pull = (a.n_recv_b + PULL_ROWS - 1) / PULL_ROWS;
+        const long long per_unit = (long long)SLOTS * SDDMM_PER_SLOT;
+        const long long n_units = (a.nnz + per_unit - 1) / per_unit;
+        const long long total = n_pull + n_units;
+        const RowsByPointer<float> arows{a.a_rows};
+        const StoreSlices store{a.sval, a.out, a.zbuf, a.Z, a.my_z, parity, a.zbase, a.zrem, a.zwidth};
+        float4* Bv = reinterpret_cast<float4*>(a.B_loc);
+        const long long ldb_v = a.ldb / 4;
+        bool pulled = n_pull == 0;
+        while (ok) {
+            const long long t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
+            if (t >= total) break;
+            if (t < n_pull) {
+                const int r0 = (int)t * PULL_ROWS;
+                const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
+                pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(c.ctrl + C_PULLS_DONE, 1);
+            } else {
+                if (!pulled) {
+                    ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
+                    pulled = true;
+                    if (!ok) break;
+                }
+                sddmm_warp_unit<float, G, R, U>(t - n_pull, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
+            }
+        }
+        main_epilogue(c, lane, nwarps);
+    }
+    if (c.phases & PH_FINISH) {
+        if (a.Z > 1) {
+            bool ok = wait_all(c, F_PART, c.contrib, c.n_contrib, W_PART);
+            // my own partials come from my own MAIN warps (same launch): wait for all of them
+            if (ok && (c.phases & PH_MAIN)) ok = wait_counter(c, C_MAIN_DONE, nwarps, W_PART);
+            const long long my_len = a.zbase + ((unsigned)a.my_z < a.zrem ? 1 : 0);
+            const int n_chunks = (int)((my_len + REDUCE_ELEMS - 1) / REDUCE_ELEMS);
+            const float* mine = a.zbuf[a.my_z] + (long long)parity * a.Z * a.zwidth;
+            while (ok) {
+                const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
+                if (t >= n_chunks) break;
+                const long long e0 = (long long)t * REDUCE_ELEMS;
+                for (long long j = e0 + lane; j < e0 + REDUCE_ELEMS && j < my_len; j += 32) {
+                    float s = 0.f;
+                    for (int z = 0; z < a.Z; ++z) s += __ldcg(mine + (long long)z * a.zwidth + j);
+                    a.out[j] = s;
+                }
+            }
+        }
+        finish_epilogue(c, lane, nwarps);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// SpMM
+// ---------------------------------------------------------------------------
+struct FusedSpmmArgs {
+    FusedComm comm;
+    int nitems;
+    const int4* items;
+    const long long* rowptr;
+    const int* colidx;
+    const float* val;
+    float* X_loc;                 // local X block [owned | pulled]
+    long long ldx;
+    int n_owned_x, n_recv_x;
+    const float4* const* x_src;   // [n_recv_x]
+    int nvec;
+    SpmmLong lg;
+    int n_owned_y;
+    float* Ypart;                 // [n_owned_y, ldp] my own partial of the rows I own
+    long long ldp;
+    float4* const* y_dst;         // [rows I do not own] slot row address at the owner (parity 0)
+    long long parity_off_v;       // float4 offset of the parity-1 slot buffer
+    float* Y;                     // [n_owned_y, ldy] result
+    long long ldy;
+    float beta;
+    const long long* cptr;        // [n_owned_y + 1] contributions per owned row
+    const int* cslot;             // slot row of each contribution, ascending source rank
+    const float* slots;           // my slot buffer (parity 0)
+    long long lds;
+};
+
+struct EmitOwnedOrPush {
+    float4* Ypart_v;
+    long long ldp_v;
+    int n_owned;
+    float4* const* y_dst;
+    long long parity_off_v;
+    __device__ __forceinline__ void operator()(int row, int v, const float4& acc) const {
+        if (row < n_owned) Ypart_v[(long long)row * ldp_v + v] = acc;
+        else __stcs(ldg_ptr(y_dst + (row - n_owned)) + parity_off_v + v, acc);
+    }
+};
+
+template <int G, int R, int U>
+__global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) {
+    const FusedComm& c = a.comm;
+    const int lane = threadIdx.x & 31;
+    const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
+    const int parity = c.epoch & 1;
+    if (c.phases & PH_START) start_phase(c);
+    if (c.phases & PH_MAIN) {
+        bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
+        const int n_pull = (a.n_recv_x + PULL_ROWS - 1) / PULL_ROWS;
+        const int total = n_pull + a.nitems;
+        float4* Xv = reinterpret_cast<float4*>(a.X_loc);
+        const long long ldx_v = a.ldx / 4;
+        const EmitOwnedOrPush emit{reinterpret_cast<float4*>(a.Ypart), a.ldp / 4, a.n_owned_y, a.y_dst,
+                                   parity ? a.parity_off_v : 0};
+        bool pulled = n_pull == 0;
+        while (ok) {
+            const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
+            if (t >= total) break;
+            if (t < n_pull) {
+                const int r0 = t * PULL_ROWS;
+                const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
+                pull_rows(r0, r1, a.x_src, Xv + (long long)a.n_owned_x * ldx_v, ldx_v, a.nvec, lane);
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(c.ctrl + C_PULLS_DONE, 1);
+            } else {
+                if (!pulled) {
+                    ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
+                    pulled = true;
+                    if (!ok) break;
+                }
+                spmm_warp_item<float, G, R, U>(__ldg(a.items + (t - n_pull)), a.rowptr, a.colidx, a.val, Xv, ldx_v,
+                                               a.nvec, emit, a.lg, lane);
+            }
+        }
+        main_epilogue(c, lane, nwarps);
+    }
+    if (c.phases & PH_FINISH) {
+        bool ok = wait_all(c, F_PART, c.contrib, c.n_contrib, W_PART);
+        // my own partial rows come from my own MAIN warps (same launch): wait for all of them
+        if (ok && (c.phases & PH_MAIN)) ok = wait_counter(c, C_MAIN_DONE, nwarps, W_PART);
+        const int n_chunks = (a.n_owned_y + REDUCE_ROWS - 1) / REDUCE_ROWS;
+        const float4* Pv = reinterpret_cast<const float4*>(a.Ypart);
+        const float4* Sv = reinterpret_cast<const float4*>(a.slots) + (parity ? a.parity_off_v : 0);
+        float4* Yv = reinterpret_cast<float4*>(a.Y);
+        const long long ldp_v = a.ldp / 4, lds_v = a.lds / 4, ldy_v = a.ldy / 4;
+        while (ok) {
+            const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
+            if (t >= n_chunks) break;
+            const int r0 = t * REDUCE_ROWS;
+            const int r1 = r0 + REDUCE_ROWS < a.n_owned_y ? r0 + REDUCE_ROWS : a.n_owned_y;
+            const int total = (r1 - r0) * a.nvec;
+            for (int e = lane; e < total; e += 32) {
+                const int row = r0 + e / a.nvec, v = e % a.nvec;
+                float4 s = __ldcg(Pv + (long long)row * ldp_v + v);
+                for (long long p = a.cptr[row]; p < a.cptr[row + 1]; ++p)
+                    vadd(s, __ldcg(Sv + (long long)a.cslot[p] * lds_v + v));
+                float4* y = Yv + (long long)row * ldy_v + v;
+                if (a.beta != 0.f) { float4 o = vscale(a.beta, *y); vadd(o, s); *y = o; }
+                else *y = s;
+            }
+        }
+        finish_epilogue(c, lane, nwarps);
+    }
+}
+
+}  // namespace sp3
+
+using namespace sp3;
+
+// Arguments arrive as a packed struct prepared by the Python front end (see
+// spcomm3d_b200/ops/fused.py for the field order); `args` points to host memory.
+SP3_API int sp3_fused_struct_sizes(int* sddmm_bytes, int* spmm_bytes, int* comm_bytes) {
+    *sddmm_bytes = (int)sizeof(FusedSddmmArgs);
+    *spmm_bytes = (int)sizeof(FusedSpmmArgs);
+    *comm_bytes = (int)sizeof(FusedComm);
+    return 0;
+}
+
+SP3_API int sp3_fused_sddmm_f32(const void* args, void* stream) {
+    FusedSddmmArgs a = *reinterpret_cast<const FusedSddmmArgs*>(args);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(a.comm.ctrl, 0, C_WORDS * sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+    int G, R;
+    pick_shape(a.nvec, &G, &R, false);
+#define SP3_FSDDMM(GG, RR)                                                                       \
+    fused_sddmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>                                                \
+        <<<persistent_blocks(fused_sddmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>, 0), 256, 0, st>>>(a)
+    SP3_DISPATCH_GR(SP3_FSDDMM)
+#undef SP3_FSDDMM
+    return (int)cudaGetLastError();
+}
+
+SP3_API int sp3_fused_spmm_f32(const void* args, void* stream) {
+    FusedSpmmArgs a = *reinterpret_cast<const FusedSpmmArgs*>(args);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(a.comm.ctrl, 0, C_WORDS * sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+    int G, R;
+    pick_shape(a.nvec, &G, &R, true);
+#define SP3_FSPMM(GG, RR)                                                                        \
+    fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>                                                 \
+        <<<persistent_blocks(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>, 0), 256, 0, st>>>(a)
+    SP3_DISPATCH_GR(SP3_FSPMM)
+#undef SP3_FSPMM
+    return (int)cudaGetLastError();
+}

@@ -13,56 +13,16 @@
 // global access is a full-width vector load of a contiguous row segment.
 // Both kernels are bound by the gathers of dense rows from HBM/L2; the
 // unroll factor U keeps U independent row loads in flight per lane.
-#include "sp3_cuda.cuh"
+#include "sp3_kernels.cuh"
 
 #include <cstdlib>
 
 namespace sp3 {
 
-constexpr int SDDMM_PER_SLOT = 32;  // nonzeros per lane group; multiple of every G
-
-template <int G> __device__ __forceinline__ unsigned group_mask(int slot) {
-    return G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (slot * G));
-}
-
 // ---------------------------------------------------------------------------
-// SDDMM: out[i] = sval[i] * <A[rowidx[i]], B[colidx[i]]>
-// A lane group of G lanes owns SDDMM_PER_SLOT consecutive nonzeros.  It reads
-// their (row, col, value) triplets G at a time with one coalesced load per
-// array and hands them round with in-group shuffles; each lane holds R
-// 16-byte vectors of the row, so a dot product costs R vector loads, 4R FMAs
-// and log2(G) shuffles per lane.  The list is sorted by row, so the A row
-// stays in registers until the row changes.  Results leave as one coalesced
-// store per G nonzeros.
+// SDDMM: out[i] = sval[i] * <A[rowidx[i]], B[colidx[i]]>; persistent grid,
+// warps stride over work units (see sddmm_warp_unit).
 // ---------------------------------------------------------------------------
-// Sums N values per lane across a group of G lanes with a halving butterfly:
-// at each step a lane keeps one half of its values and hands the other half
-// to its partner, so the whole reduction costs N-1 + log2(G/N) shuffles instead
-// of N*log2(G).  N <= G, both powers of two.  On return v[0] of lane gl holds
-// the group total of value number gl / (G/N).
-template <typename T, int G, int N>
-__device__ __forceinline__ void group_transpose_reduce(T (&v)[N], unsigned gmask, int gl) {
-    int n = N;
-#pragma unroll
-    for (int m = G / 2; m > 0; m >>= 1) {
-        if (n > 1) {
-            const int half = n >> 1;
-            const bool upper = (gl & m) != 0;
-#pragma unroll
-            for (int t = 0; t < N / 2; ++t) {
-                if (t < half) {
-                    const T send = upper ? v[t] : v[t + half];
-                    const T keep = upper ? v[t + half] : v[t];
-                    v[t] = keep + __shfl_xor_sync(gmask, send, m, G);
-                }
-            }
-            n = half;
-        } else {
-            v[0] += __shfl_xor_sync(gmask, v[0], m, G);
-        }
-    }
-}
-
 template <typename T, int G, int R, int U>
 __global__ void __launch_bounds__(256)
 sddmm_vec_kernel(long long nnz, const int* __restrict__ rowidx, const int* __restrict__ colidx,
@@ -70,62 +30,14 @@ sddmm_vec_kernel(long long nnz, const int* __restrict__ rowidx, const int* __res
                  const T* __restrict__ B, long long ldb, int nvec, T* __restrict__ out) {
     using V = typename Vec<T>::type;
     constexpr int SLOTS = 32 / G;
-    constexpr int UU = U < G ? U : G;
     const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-    const int lane = threadIdx.x & 31, slot = lane / G, gl = lane % G;
-    const unsigned gmask = group_mask<G>(slot);
-    const V* Av = reinterpret_cast<const V*>(A);
-    const V* Bv = reinterpret_cast<const V*>(B);
-    const long long lda_v = lda / Vec<T>::N, ldb_v = ldb / Vec<T>::N;
-    for (long long warp = warp0; warp * SLOTS * (long long)SDDMM_PER_SLOT < nnz; warp += nwarps) {
-        const long long begin = (warp * SLOTS + slot) * (long long)SDDMM_PER_SLOT;
-        int cur_row = -1;
-        V a[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) a[r] = vzero((V*)nullptr);
-        for (int base = 0; base < SDDMM_PER_SLOT; base += G) {
-            const long long i = begin + base + gl;
-            const bool ok = i < nnz;
-            const int my_r = ok ? __ldg(rowidx + i) : -1;
-            const int my_c = ok ? __ldg(colidx + i) : -1;
-            T acc[G];
-#pragma unroll
-            for (int j = 0; j < G; j += UU) {
-                int rr[UU], cc[UU];
-                V b[UU][R];
-#pragma unroll
-                for (int u = 0; u < UU; ++u) {
-                    rr[u] = __shfl_sync(gmask, my_r, j + u, G);
-                    cc[u] = __shfl_sync(gmask, my_c, j + u, G);
-                }
-#pragma unroll
-                for (int u = 0; u < UU; ++u)
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const int v = gl + r * G;
-                        b[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Bv + (long long)cc[u] * ldb_v + v) : vzero((V*)nullptr);
-                    }
-#pragma unroll
-                for (int u = 0; u < UU; ++u) {
-                    if (rr[u] >= 0 && rr[u] != cur_row) {
-                        cur_row = rr[u];
-#pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            const int v = gl + r * G;
-                            a[r] = v < nvec ? __ldg(Av + (long long)cur_row * lda_v + v) : vzero((V*)nullptr);
-                        }
-                    }
-                    T d = 0;
-#pragma unroll
-                    for (int r = 0; r < R; ++r) d += vdot(a[r], b[u][r]);
-                    acc[j + u] = d;
-                }
-            }
-            group_transpose_reduce<T, G, G>(acc, gmask, gl);  // lane gl now holds nonzero gl of the batch
-            if (ok) out[i] = sval ? acc[0] * __ldg(sval + i) : acc[0];
-        }
-    }
+    const int lane = threadIdx.x & 31;
+    const RowsByStride<T> arows{reinterpret_cast<const V*>(A), lda / Vec<T>::N};
+    const StoreLocal<T> store{out, sval};
+    for (long long unit = warp0; unit * SLOTS * (long long)SDDMM_PER_SLOT < nnz; unit += nwarps)
+        sddmm_warp_unit<T, G, R, U>(unit, nnz, rowidx, colidx, arows, reinterpret_cast<const V*>(B),
+                                    ldb / Vec<T>::N, nvec, store, lane);
 }
 
 // Any k, any leading dimension: one warp per nonzero slot, scalar loads.
@@ -149,211 +61,23 @@ sddmm_scalar_kernel(long long nnz, const int* __restrict__ rowidx, const int* __
 }
 
 // ---------------------------------------------------------------------------
-// SpMM over work items (one warp per item).
-//   rows item   {row_begin, row_end, 0, -1}: lane groups take whole rows.
-//   piece item  {row, nnz_begin, nnz_end, long_row_slot}: a slice of a long
-//               row; the warp's partial goes to the carry scratch and the
-//               warp that completes the row adds the pieces in piece order
-//               (fixed order => bitwise reproducible) and writes the row.
-// Y[row] = beta * Y[row] + sum.  Rows without nonzeros are covered by rows
-// items, so beta is applied to every row exactly once.
+// SpMM over work items (see spmm_warp_item): Y[row] = beta * Y[row] + sum.
+// Rows without nonzeros are covered by rows items, so beta is applied to
+// every row exactly once.
 // ---------------------------------------------------------------------------
-struct SpmmLong {
-    const int* first_piece;  // [nlong] first carry slot of each long row
-    const int* npieces;      // [nlong]
-    int* counters;           // [nlong] zero at launch; reset by the finishing warp
-    void* carry;             // [total pieces, ldc] scratch
-    long long ldc;           // elements per carry row
-    int piece_len;           // nonzeros per piece
-};
-
-// Adds val[q] * X[colidx[q]] for q in [p0, p1) taken in batches of G (one
-// coalesced index/value load per batch, broadcast inside the lane group);
-// consecutive batches of this group are `batch_stride` apart.
-template <typename T, int G, int R, int U>
-__device__ __forceinline__ void spmm_accumulate(typename Vec<T>::type (&acc)[R], long long p0, long long p1,
-                                                int batch_stride, unsigned gmask,
-                                                const int* __restrict__ colidx, const T* __restrict__ val,
-                                                const typename Vec<T>::type* __restrict__ Xv, long long ldx_v,
-                                                int gl, int nvec) {
-    using V = typename Vec<T>::type;
-    constexpr int UU = U < G ? U : G;
-    for (long long base = p0; base < p1; base += batch_stride) {
-        const long long q = base + gl;
-        const bool ok = q < p1;
-        const int my_c = ok ? __ldg(colidx + q) : -1;
-        const T my_v = ok ? __ldg(val + q) : (T)0;
-        const int n = (p1 - base) < G ? (int)(p1 - base) : G;
-        for (int j = 0; j < n; j += UU) {
-            int cc[UU];
-            T vv[UU];
-#pragma unroll
-            for (int u = 0; u < UU; ++u) {
-                cc[u] = __shfl_sync(gmask, my_c, j + u, G);
-                vv[u] = __shfl_sync(gmask, my_v, j + u, G);
-            }
-            V x[UU][R];
-#pragma unroll
-            for (int u = 0; u < UU; ++u)
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int v = gl + r * G;
-                    x[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Xv + (long long)cc[u] * ldx_v + v) : vzero((V*)nullptr);
-                }
-#pragma unroll
-            for (int u = 0; u < UU; ++u)
-#pragma unroll
-                for (int r = 0; r < R; ++r) vfma(acc[r], vv[u], x[u][r]);
-        }
-    }
-}
-
-// Rows [r0, r1) of the CSR matrix as one flat stream of nonzeros: entries are
-// fetched G at a time (the next batch is requested before the current one is
-// consumed), U dense rows are in flight per lane, and the accumulator is
-// written out whenever the stream crosses into the next row.  Rows without
-// nonzeros are written too (beta * Y).  One lane group runs this alone, so no
-// atomics are involved and the result is reproducible.
-template <typename T, int G, int R, int U>
-__device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long* __restrict__ rowptr,
-                                                 const int* __restrict__ colidx, const T* __restrict__ val,
-                                                 const typename Vec<T>::type* __restrict__ Xv, long long ldx_v,
-                                                 typename Vec<T>::type* __restrict__ Yv, long long ldy_v, T beta,
-                                                 unsigned gmask, int gl, int nvec) {
-    using V = typename Vec<T>::type;
-    constexpr int UU = U < G ? U : G;
-    if (r0 >= r1) return;
-    const long long qend = rowptr[r1];
-    long long base = rowptr[r0];
-    int row = r0;
-    long long row_end = rowptr[r0 + 1];
-    V acc[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = vzero((V*)nullptr);
-    auto flush = [&](int rw) {
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int v = gl + r * G;
-            if (v < nvec) {
-                V* y = Yv + (long long)rw * ldy_v + v;
-                if (beta != (T)0) { V o = vscale(beta, *y); vadd(o, acc[r]); *y = o; }
-                else *y = acc[r];
-            }
-            acc[r] = vzero((V*)nullptr);
-        }
-    };
-    int nxt_c = (base + gl < qend) ? __ldg(colidx + base + gl) : -1;
-    T nxt_v = (base + gl < qend) ? __ldg(val + base + gl) : (T)0;
-    while (base < qend) {
-        const int my_c = nxt_c;
-        const T my_v = nxt_v;
-        const long long nb = base + G;
-        nxt_c = (nb + gl < qend) ? __ldg(colidx + nb + gl) : -1;
-        nxt_v = (nb + gl < qend) ? __ldg(val + nb + gl) : (T)0;
-        const int n = (qend - base) < G ? (int)(qend - base) : G;
-        for (int j = 0; j < n; j += UU) {
-            int cc[UU];
-            T vv[UU];
-#pragma unroll
-            for (int u = 0; u < UU; ++u) {
-                cc[u] = __shfl_sync(gmask, my_c, j + u, G);
-                vv[u] = __shfl_sync(gmask, my_v, j + u, G);
-            }
-            V x[UU][R];
-#pragma unroll
-            for (int u = 0; u < UU; ++u)
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int v = gl + r * G;
-                    x[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Xv + (long long)cc[u] * ldx_v + v) : vzero((V*)nullptr);
-                }
-#pragma unroll
-            for (int u = 0; u < UU; ++u) {
-                if (j + u < n) {
-                    const long long q = base + j + u;
-                    while (q >= row_end) {
-                        flush(row);
-                        ++row;
-                        row_end = rowptr[row + 1];
-                    }
-#pragma unroll
-                    for (int r = 0; r < R; ++r) vfma(acc[r], vv[u], x[u][r]);
-                }
-            }
-        }
-        base = nb;
-    }
-    while (row < r1) {
-        flush(row);
-        ++row;
-    }
-}
-
 template <typename T, int G, int R, int U>
 __global__ void __launch_bounds__(256)
 spmm_items_kernel(int nitems, const int4* __restrict__ items, const long long* __restrict__ rowptr,
                   const int* __restrict__ colidx, const T* __restrict__ val, const T* __restrict__ X,
                   long long ldx, int nvec, T beta, T* __restrict__ Y, long long ldy, SpmmLong lg) {
     using V = typename Vec<T>::type;
-    constexpr int SLOTS = 32 / G;
     const int warp0 = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
-    const int lane = threadIdx.x & 31, slot = lane / G, gl = lane % G;
-    const unsigned gmask = group_mask<G>(slot);
-    const V* Xv = reinterpret_cast<const V*>(X);
-    V* Yv = reinterpret_cast<V*>(Y);
-    const long long ldx_v = ldx / Vec<T>::N, ldy_v = ldy / Vec<T>::N;
-    for (int it = warp0; it < nitems; it += nwarps) {
-    const int4 item = __ldg(items + it);
-    V acc[R];
-    if (item.w < 0) {
-        const int nr = item.y - item.x;
-        const int r0 = item.x + (int)(((long long)nr * slot) / SLOTS);
-        const int r1 = item.x + (int)(((long long)nr * (slot + 1)) / SLOTS);
-        spmm_rows_stream<T, G, R, U>(r0, r1, rowptr, colidx, val, Xv, ldx_v, Yv, ldy_v, beta, gmask, gl, nvec);
-        continue;
-    }
-    // piece of a long row: the warp reads 32 consecutive entries per step, each
-    // group takes its G of them; groups are combined afterwards
-#pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = vzero((V*)nullptr);
-    spmm_accumulate<T, G, R, U>(acc, (long long)item.y + slot * G, item.z, 32, gmask, colidx, val, Xv, ldx_v, gl, nvec);
-#pragma unroll
-    for (int m = G; m < 32; m <<= 1)
-#pragma unroll
-        for (int r = 0; r < R; ++r) vadd(acc[r], shfl_xor_vec(acc[r], m));
-    const int lr = item.w, row = item.x;
-    const int first = __ldg(lg.first_piece + lr), np = __ldg(lg.npieces + lr);
-    const int piece = first + (int)((item.y - rowptr[row]) / lg.piece_len);
-    V* carry = reinterpret_cast<V*>(lg.carry);
-    const long long ldc_v = lg.ldc / Vec<T>::N;
-    if (slot == 0)
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int v = gl + r * G;
-            if (v < nvec) __stcg(carry + (long long)piece * ldc_v + v, acc[r]);
-        }
-    __threadfence();
-    __syncwarp();
-    int old = 0;
-    if (lane == 0) old = atomicAdd(lg.counters + lr, 1);
-    old = __shfl_sync(0xffffffffu, old, 0);
-    if (old != np - 1) continue;
-    __threadfence();
-    if (slot == 0) {
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int v = gl + r * G;
-            if (v >= nvec) continue;
-            V s = vzero((V*)nullptr);
-            for (int j = 0; j < np; ++j) vadd(s, __ldcg(carry + (long long)(first + j) * ldc_v + v));
-            V* y = Yv + (long long)row * ldy_v + v;
-            if (beta != (T)0) { V o = vscale(beta, *y); vadd(o, s); *y = o; }
-            else *y = s;
-        }
-    }
-    if (lane == 0) lg.counters[lr] = 0;
-    }
+    const int lane = threadIdx.x & 31;
+    const EmitLocal<T> emit{reinterpret_cast<V*>(Y), ldy / Vec<T>::N, beta};
+    for (int it = warp0; it < nitems; it += nwarps)
+        spmm_warp_item<T, G, R, U>(__ldg(items + it), rowptr, colidx, val, reinterpret_cast<const V*>(X),
+                                   ldx / Vec<T>::N, nvec, emit, lg, lane);
 }
 
 // Any k / leading dimension: one warp per row, scalar loads, no schedule.
@@ -497,52 +221,6 @@ __global__ void touch_masks_kernel(long long nnz, const int* __restrict__ rows, 
 }
 
 // ---- dispatch ---------------------------------------------------------------
-// Lane-group shape for a row of `nvec` 16-byte vectors: R vectors per lane
-// (default 4, overridable for tuning with SP3_VEC_PER_LANE=1|2|4|8), G lanes.
-inline int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return e ? atoi(e) : dflt;
-}
-
-// Resident blocks of 256 threads for a persistent launch of `kernel`.
-template <typename K>
-unsigned persistent_blocks(K kernel, long long needed) {
-    int dev = 0, sms = 0, per_sm = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0);
-    static const int mult = env_int("SP3_PERSIST", 1);
-    long long b = mult > 0 ? (long long)sms * (per_sm > 0 ? per_sm : 1) * mult : needed;
-    if (b > needed) b = needed;
-    return (unsigned)(b > 0 ? b : 1);
-}
-
-// SDDMM (spmm == false) runs best with about 16 lanes per row and 2-4 vectors
-// per lane; SpMM with as many lanes per row as the row has vectors (measured
-// on B200, R-MAT scale 20, k = 32..256).
-inline void pick_shape(int nvec, int* G, int* R, bool spmm) {
-    static const int forced = env_int("SP3_VEC_PER_LANE", 0);
-    int r = 1;
-    if (!spmm) { r = 2; while (nvec > 16 * r && r < 8) r <<= 1; }
-    if (forced > 0) r = forced;
-    while (r > 1 && r > nvec) r >>= 1;
-    int g = pick_group((nvec + r - 1) / r);
-    while (g * r < nvec) r <<= 1;  // nvec > 32 * r
-    *G = g; *R = r;
-}
-
-#define SP3_DISPATCH_GR(MACRO)                                                          \
-    switch (R) {                                                                        \
-        case 1: switch (G) { case 1: MACRO(1, 1); break; case 2: MACRO(2, 1); break; case 4: MACRO(4, 1); break; \
-                             case 8: MACRO(8, 1); break; case 16: MACRO(16, 1); break; default: MACRO(32, 1); } break; \
-        case 2: switch (G) { case 1: MACRO(1, 2); break; case 2: MACRO(2, 2); break; case 4: MACRO(4, 2); break; \
-                             case 8: MACRO(8, 2); break; case 16: MACRO(16, 2); break; default: MACRO(32, 2); } break; \
-        case 4: switch (G) { case 1: MACRO(1, 4); break; case 2: MACRO(2, 4); break; case 4: MACRO(4, 4); break; \
-                             case 8: MACRO(8, 4); break; case 16: MACRO(16, 4); break; default: MACRO(32, 4); } break; \
-        default: switch (G) { case 1: MACRO(1, 8); break; case 2: MACRO(2, 8); break; case 4: MACRO(4, 8); break; \
-                              case 8: MACRO(8, 8); break; case 16: MACRO(16, 8); break; default: MACRO(32, 8); } break; \
-    }
-
 template <typename T>
 int launch_sddmm(long long nnz, const int* ri, const int* ci, const T* sv, const T* A, long long lda, const T* B,
                  long long ldb, int k, T* out, cudaStream_t st) {
@@ -560,15 +238,10 @@ int launch_sddmm(long long nnz, const int* ri, const int* ci, const T* sv, const
     const long long slots = (nnz + SDDMM_PER_SLOT - 1) / SDDMM_PER_SLOT;
     const long long warps = (slots + (32 / G) - 1) / (32 / G);
     const long long needed = (warps + 7) / 8;
-    static const int unroll = env_int("SP3_UNROLL", 4);
-#define SP3_SDDMM(GG, RR)                                                                                       \
-    if (unroll >= 8 && RR <= 2)                                                                                 \
-        sddmm_vec_kernel<T, GG, RR, 8><<<persistent_blocks(sddmm_vec_kernel<T, GG, RR, 8>, needed), 256, 0, st>>>( \
-            nnz, ri, ci, sv, A, lda, B, ldb, nvec, out);                                                        \
-    else                                                                                                        \
-        sddmm_vec_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>                                                          \
-            <<<persistent_blocks(sddmm_vec_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>, needed), 256, 0, st>>>(        \
-                nnz, ri, ci, sv, A, lda, B, ldb, nvec, out)
+#define SP3_SDDMM(GG, RR)                                                                                      \
+    sddmm_vec_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>                                                             \
+        <<<persistent_blocks(sddmm_vec_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>, needed), 256, 0, st>>>(           \
+            nnz, ri, ci, sv, A, lda, B, ldb, nvec, out)
     SP3_DISPATCH_GR(SP3_SDDMM)
 #undef SP3_SDDMM
     return (int)cudaGetLastError();
@@ -589,15 +262,10 @@ int launch_spmm(int nrows, int nitems, const int4* items, const long long* rowpt
     int G, R;
     pick_shape(nvec, &G, &R, true);
     const long long needed = ((long long)nitems + 7) / 8;
-    static const int unroll = env_int("SP3_UNROLL", 4);
-#define SP3_SPMM(GG, RR)                                                                                         \
-    if (unroll >= 8 && RR <= 2)                                                                                  \
-        spmm_items_kernel<T, GG, RR, 8><<<persistent_blocks(spmm_items_kernel<T, GG, RR, 8>, needed), 256, 0, st>>>( \
-            nitems, items, rowptr, ci, val, X, ldx, nvec, beta, Y, ldy, lg);                                     \
-    else                                                                                                         \
-        spmm_items_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>                                                          \
-            <<<persistent_blocks(spmm_items_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>, needed), 256, 0, st>>>(        \
-                nitems, items, rowptr, ci, val, X, ldx, nvec, beta, Y, ldy, lg)
+#define SP3_SPMM(GG, RR)                                                                                       \
+    spmm_items_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>                                                            \
+        <<<persistent_blocks(spmm_items_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>, needed), 256, 0, st>>>(          \
+            nitems, items, rowptr, ci, val, X, ldx, nvec, beta, Y, ldy, lg)
     SP3_DISPATCH_GR(SP3_SPMM)
 #undef SP3_SPMM
     return (int)cudaGetLastError();

@@ -105,6 +105,11 @@ __device__ __forceinline__ bool wait_ge_gpu(const int* flag, int want, unsigned 
     }
 }
 
+// read-only load of a pointer-table entry
+template <typename P> __device__ __forceinline__ P* ldg_ptr(P* const* slot) {
+    return reinterpret_cast<P*>(__ldg(reinterpret_cast<const unsigned long long*>(slot)));
+}
+
 // lanes-per-row choice: smallest power of two G (<= 32) with G * VN >= k,
 // R = vectors per lane.
 __host__ __device__ inline int pick_group(int nvec) {

@@ -46,7 +46,7 @@ class _Dist3DOp:
     kernel = "?"
 
     def __init__(self, plan: RankPlan, groups: MeshGroups | None, k: int, dtype=torch.float32,
-                 device="cpu", variant: str = "sparseNRB"):
+                 device="cpu", variant: str = "sparseNRB", emulated: bool = False):
         if variant not in VARIANTS:
             raise ValueError(f"variant must be one of {VARIANTS}")
         self.plan, self.groups, self.k, self.dtype, self.variant = plan, groups, k, dtype, variant
@@ -55,7 +55,7 @@ class _Dist3DOp:
         self.k_off, self.k_loc = split_k(k, self.mesh.Z, plan.coords[2])
         self.timer = PhaseTimer(self.device)
         self.last_times: dict = {}
-        if groups is None and self.mesh.size != 1:
+        if groups is None and self.mesh.size != 1 and not emulated:
             raise ValueError("a multi-rank mesh needs MeshGroups")
         if variant == "fused" and self.device.type != "cuda":
             raise ValueError("the fused variant runs on GPUs only")
@@ -99,6 +99,8 @@ class _Dist3DOp:
     def _finish(self):
         if not self.timer.enabled:
             return None
+        if self.variant == "fused":
+            self._fused.check()
         self.last_times = self.timer.collect()
         t = self.last_times
         t["total"] = t.get("comm1", 0.0) + t.get("comp", 0.0) + t.get("comm2", 0.0)
@@ -121,7 +123,7 @@ class DistSDDMM(_Dist3DOp):
     kernel = "sddmm"
 
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
-        super().__init__(plan, groups, k, dtype, device, variant)
+        super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSDDMM
@@ -190,7 +192,7 @@ class DistSpMM(_Dist3DOp):
     kernel = "spmm"
 
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
-        super().__init__(plan, groups, k, dtype, device, variant)
+        super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSpMM

@@ -1,0 +1,312 @@
+"""Front end of the fused compute+communication kernels (csrc/kernels/fused_ops.cu).
+
+`FusedSDDMM` / `FusedSpMM` own the symmetric heap of one distributed op, turn
+its plan into the pointer tables the kernel needs (absolute addresses of dense
+rows in the owners' heaps, of value buffers along the Z fiber, of partial-row
+slots at the row owners) and launch one persistent kernel per run.
+
+These are the product path that replaces the reference's message pipelines
+(src/distributed_comp.cpp:17-76, 141-284): no staging buffers, no library
+collective; remote rows are loaded, and partial results stored, by the kernel
+itself through NVLink peer addresses.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from ..parallel.symm import ALIGN, IpcFabric, SymmHeap, _align
+from ..utils import native
+from . import cuda_ops
+
+MAX_RANKS = 64
+F_KINDS = 3
+PH_START, PH_MAIN, PH_FINISH = 1, 2, 4
+PH_ALL = 7
+_SITES = {1: "READY flag of a rank whose memory is read", 2: "local pull counter",
+          3: "PART flag (partial results) of a contributing rank", 4: "DONE flag of a reader", 100: "flag"}
+
+P = C.c_void_p
+
+
+class _Comm(C.Structure):
+    _fields_ = [("me", C.c_int), ("epoch", C.c_int), ("phases", C.c_int), ("timeout_ns", C.c_ulonglong),
+                ("status", P), ("ctrl", P), ("pad", P), ("peer_pad", P), ("read_from", P), ("readers", P),
+                ("push_to", P), ("contrib", P), ("n_read", C.c_int), ("n_readers", C.c_int),
+                ("n_push", C.c_int), ("n_contrib", C.c_int)]
+
+
+class _SddmmArgs(C.Structure):
+    _fields_ = [("comm", _Comm), ("nnz", C.c_longlong), ("rowidx", P), ("colidx", P), ("sval", P),
+                ("a_rows", P), ("B_loc", P), ("ldb", C.c_longlong), ("n_owned_b", C.c_int),
+                ("n_recv_b", C.c_int), ("b_src", P), ("nvec", C.c_int), ("Z", C.c_int), ("my_z", C.c_int),
+                ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P)]
+
+
+class _SpmmLong(C.Structure):
+    _fields_ = [("first_piece", P), ("npieces", P), ("counters", P), ("carry", P), ("ldc", C.c_longlong),
+                ("piece_len", C.c_int)]
+
+
+class _SpmmArgs(C.Structure):
+    _fields_ = [("comm", _Comm), ("nitems", C.c_int), ("items", P), ("rowptr", P), ("colidx", P), ("val", P),
+                ("X_loc", P), ("ldx", C.c_longlong), ("n_owned_x", C.c_int), ("n_recv_x", C.c_int),
+                ("x_src", P), ("nvec", C.c_int), ("lg", _SpmmLong), ("n_owned_y", C.c_int), ("Ypart", P),
+                ("ldp", C.c_longlong), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
+                ("ldy", C.c_longlong), ("beta", C.c_float), ("cptr", P), ("cslot", P), ("slots", P),
+                ("lds", C.c_longlong)]
+
+
+_checked_layout = False
+
+
+def _check_layout():
+    global _checked_layout
+    if _checked_layout:
+        return
+    a, b, c = C.c_int(), C.c_int(), C.c_int()
+    native.cuda().sp3_fused_struct_sizes(C.byref(a), C.byref(b), C.byref(c))
+    if (a.value, b.value, c.value) != (C.sizeof(_SddmmArgs), C.sizeof(_SpmmArgs), C.sizeof(_Comm)):
+        raise RuntimeError("argument struct layout differs between Python and the kernel library: "
+                           f"{(a.value, b.value, c.value)} vs "
+                           f"{(C.sizeof(_SddmmArgs), C.sizeof(_SpmmArgs), C.sizeof(_Comm))}")
+    _checked_layout = True
+
+
+class FusedStatusError(RuntimeError):
+    pass
+
+
+def _peer_ranks(plan, side: str):
+    """World rank of every peer along a side of the plan's mesh position."""
+    x, y, z = plan.coords
+    m = plan.mesh
+    if side == "row":
+        return [m.rank_of(x, j, z) for j in range(m.Y)]
+    if side == "col":
+        return [m.rank_of(i, y, z) for i in range(m.X)]
+    return [m.rank_of(x, y, k) for k in range(m.Z)]
+
+
+class _FusedBase:
+    def __init__(self, op, heap: SymmHeap | None, fabric, timeout_s: float):
+        _check_layout()
+        self.op, self.plan = op, op.plan
+        self.device = op.device
+        self.k_loc = op.k_loc
+        if op.dtype != torch.float32:
+            raise ValueError("fused kernels are fp32")
+        if self.k_loc % 4 or self.k_loc == 0 or self.k_loc > 1024:
+            raise ValueError(f"fused kernels need k/Z to be a multiple of 4 (got {self.k_loc})")
+        if self.plan.mesh.size > MAX_RANKS:
+            raise ValueError(f"fused kernels support at most {MAX_RANKS} ranks")
+        self.row_bytes = self.k_loc * 4
+        self.nvec = self.k_loc // 4
+        if heap is None:
+            if fabric is None:
+                fabric = IpcFabric(device=self.device)
+            heap = fabric.heap(self.region_sizes(self.plan, self.k_loc))
+        self.heap = heap
+        self.rank = self.plan.rank
+        self.epoch = 0
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.ctrl = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.pad = heap.view("pad", torch.int32, (F_KINDS * MAX_RANKS,))
+        self.peer_pad = self._dev_i64([heap.addr("pad", r) for r in range(heap.world)])
+        self._keep = []
+
+    def _dev_i64(self, values):
+        return torch.from_numpy(np.asarray(values, dtype=np.int64).reshape(-1)).to(self.device)
+
+    def _dev_i32(self, values):
+        return torch.from_numpy(np.asarray(values, dtype=np.int32).reshape(-1)).to(self.device)
+
+    def _fill_comm(self, comm: _Comm, read_from, readers, push_to, contrib):
+        lists = []
+        for name, ranks in (("read_from", read_from), ("readers", readers), ("push_to", push_to),
+                            ("contrib", contrib)):
+            t = self._dev_i32(sorted(set(int(r) for r in ranks)) or [0])
+            n = len(set(ranks))
+            lists.append(t)
+            setattr(comm, name, t.data_ptr())
+            setattr(comm, {"read_from": "n_read", "readers": "n_readers", "push_to": "n_push",
+                           "contrib": "n_contrib"}[name], n)
+        self._keep.append(lists)
+        comm.me = self.rank
+        comm.timeout_ns = self.timeout_ns
+        comm.status = self.status.data_ptr()
+        comm.ctrl = self.ctrl.data_ptr()
+        comm.pad = self.pad.data_ptr()
+        comm.peer_pad = self.peer_pad.data_ptr()
+
+    def _side_tables(self, side, region):
+        """(addresses of every local row in its owner's heap, addresses of the rows to pull)."""
+        h, rb = self.heap, self.row_bytes
+        ranks = np.asarray(_peer_ranks(self.plan, side.side), dtype=np.int64)
+        base = np.asarray(h.peer_base, dtype=np.int64) + h.offsets[region]
+        own = base[self.rank] + np.arange(side.n_owned, dtype=np.int64) * rb
+        need = base[ranks[side.recv_peer]] + side.recv_src_idx.astype(np.int64) * rb
+        return own, need
+
+    def set_timeout(self, seconds: float):
+        self.timeout_ns = int(seconds * 1e9)
+        self.args.comm.timeout_ns = self.timeout_ns
+
+    def check(self):
+        """Synchronises and raises if the last launches recorded a status."""
+        torch.cuda.synchronize(self.device)
+        st = self.status.tolist()
+        if st[0] != 0:
+            self.status.zero_()
+            what = {1: "bad index", 2: "wait timed out"}.get(st[0], f"code {st[0]}")
+            raise FusedStatusError(f"fused kernel on rank {self.rank}: {what} at {_SITES.get(st[1], st[1])}, "
+                                   f"peer/slot {st[2]}, observed {st[3]} (epoch {self.epoch})")
+
+    def _launch(self, fn, phases):
+        self.args.comm.phases = phases
+        self.args.comm.epoch = self.epoch
+        rc = fn(C.byref(self.args), torch.cuda.current_stream(self.device).cuda_stream)
+        cuda_ops.LAUNCHES += 1
+        if rc != 0:
+            raise RuntimeError(f"fused kernel launch failed: CUDA error {rc}")
+
+
+class FusedSDDMM(_FusedBase):
+    @staticmethod
+    def region_sizes(plan, k_loc: int) -> dict:
+        rb = k_loc * 4
+        Z = plan.mesh.Z
+        zwidth = plan.nnz // Z + (1 if plan.nnz % Z else 0)
+        return {"pad": F_KINDS * MAX_RANKS * 4, "A": plan.row.n_owned * rb, "B": plan.col.n_local * rb,
+                "zbuf": 2 * Z * zwidth * 4 if Z > 1 else 0}
+
+    def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0):
+        super().__init__(op, heap, fabric, timeout_s)
+        p, h, k = self.plan, self.heap, self.k_loc
+        Z, z = p.mesh.Z, p.coords[2]
+        # A: only my owned rows live here (peers read them in place); the op's A_loc is that block
+        self.A_loc = h.view("A", torch.float32, (p.row.n_owned, k))
+        self.B_loc = h.view("B", torch.float32, (p.col.n_local, k))
+        a_own, a_need = self._side_tables(p.row, "A")
+        _, b_need = self._side_tables(p.col, "B")
+        self.a_rows = self._dev_i64(np.concatenate([a_own, a_need]))
+        self.b_src = self._dev_i64(b_need if b_need.size else [0])
+        self.zwidth = p.nnz // Z + (1 if p.nnz % Z else 0)
+        fiber = _peer_ranks(p, "fiber")
+        self.zbuf_ptrs = self._dev_i64([h.addr("zbuf", r) for r in fiber])
+        self.out_len = p.nnz if Z == 1 else p.owned_nnz_slice()[1]
+        self.out = torch.zeros(max(self.out_len, 1), dtype=torch.float32, device=self.device)
+        a = self.args = _SddmmArgs()
+        row_r, col_r = _peer_ranks(p, "row"), _peer_ranks(p, "col")
+        read_from = [row_r[q] for q in range(p.row.npeers) if p.row.recv_counts[q] > 0] + \
+                    [col_r[q] for q in range(p.col.npeers) if p.col.recv_counts[q] > 0]
+        readers = [row_r[q] for q in range(p.row.npeers) if p.row.send_counts[q] > 0] + \
+                  [col_r[q] for q in range(p.col.npeers) if p.col.send_counts[q] > 0]
+        others = [r for r in fiber if r != self.rank] if Z > 1 else []
+        self._fill_comm(a.comm, read_from, readers, others, others)
+        a.nnz = p.nnz
+        a.rowidx, a.colidx, a.sval = op.rowidx.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
+        a.a_rows = self.a_rows.data_ptr()
+        a.B_loc, a.ldb = self.B_loc.data_ptr(), k
+        a.n_owned_b, a.n_recv_b = p.col.n_owned, p.col.n_recv
+        a.b_src = self.b_src.data_ptr()
+        a.nvec = self.nvec
+        a.Z, a.my_z = Z, z
+        a.zbase, a.zrem = p.nnz // Z, p.nnz % Z
+        a.zwidth = self.zwidth
+        a.zbuf = self.zbuf_ptrs.data_ptr()
+        a.out = self.out.data_ptr()
+
+    def launch(self, phases=PH_ALL, new_epoch=True):
+        if new_epoch:
+            self.epoch += 1
+        self._launch(native.cuda().sp3_fused_sddmm_f32, phases)
+
+    def run(self):
+        self.launch()
+        return self.out[:self.out_len]
+
+
+class FusedSpMM(_FusedBase):
+    @staticmethod
+    def region_sizes(plan, k_loc: int) -> dict:
+        rb = k_loc * 4
+        return {"pad": F_KINDS * MAX_RANKS * 4, "X": plan.col.n_local * rb,
+                "slots": 2 * _align(plan.row.n_send * rb)}
+
+    def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0):
+        super().__init__(op, heap, fabric, timeout_s)
+        p, h, k, rb = self.plan, self.heap, self.k_loc, self.row_bytes
+        rp = p.row
+        self.X_loc = h.view("X", torch.float32, (p.col.n_local, k))
+        # the op's Y_loc is only used for its owned rows here: my own partial of the rows I own
+        self.Y_loc = torch.zeros(max(rp.n_owned, 1), k, dtype=torch.float32, device=self.device)
+        _, x_need = self._side_tables(p.col, "X")
+        self.x_src = self._dev_i64(x_need if x_need.size else [0])
+        half = h.sizes["slots"] // 2
+        assert half % 16 == 0
+        row_r, col_r = _peer_ranks(p, "row"), _peer_ranks(p, "col")
+        # destination of every partial row I do not own: its slot in the owner's heap
+        roff = rp.recv_offsets()
+        i_in_seg = np.arange(rp.n_recv, dtype=np.int64) - roff[rp.recv_peer]
+        slot_row = rp.push_offset[rp.recv_peer] + i_in_seg
+        base = np.asarray(h.peer_base, dtype=np.int64) + h.offsets["slots"]
+        y_dst = base[np.asarray(row_r, dtype=np.int64)[rp.recv_peer]] + slot_row * rb
+        self.y_dst = self._dev_i64(y_dst if y_dst.size else [0])
+        # contributions to my owned rows: slot rows grouped by owned row, ascending source
+        order = np.argsort(rp.send_idx, kind="stable")
+        cptr = np.zeros(rp.n_owned + 1, np.int64)
+        np.cumsum(np.bincount(rp.send_idx, minlength=rp.n_owned), out=cptr[1:])
+        self.cptr = self._dev_i64(cptr)
+        self.cslot = self._dev_i32(order if order.size else [0])
+        self.sched = cuda_ops.SpmmSchedule(op.rowptr)
+        carry, ldc = self.sched.carry_for(k, torch.float32, self.device)
+        self.slots = h.view("slots", torch.float32, (h.sizes["slots"] // 4,))
+        a = self.args = _SpmmArgs()
+        read_from = [col_r[q] for q in range(p.col.npeers) if p.col.recv_counts[q] > 0]
+        readers = [col_r[q] for q in range(p.col.npeers) if p.col.send_counts[q] > 0]
+        push_to = [row_r[q] for q in range(rp.npeers) if rp.recv_counts[q] > 0]
+        contrib = [row_r[q] for q in range(rp.npeers) if rp.send_counts[q] > 0]
+        self._fill_comm(a.comm, read_from, readers, push_to, contrib)
+        a.nitems, a.items = self.sched.items.shape[0], self.sched.items.data_ptr()
+        a.rowptr, a.colidx, a.val = op.rowptr.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
+        a.X_loc, a.ldx = self.X_loc.data_ptr(), k
+        a.n_owned_x, a.n_recv_x = p.col.n_owned, p.col.n_recv
+        a.x_src = self.x_src.data_ptr()
+        a.nvec = self.nvec
+        a.lg.first_piece, a.lg.npieces = self.sched.first.data_ptr(), self.sched.npieces.data_ptr()
+        a.lg.counters = self.sched.counters.data_ptr()
+        a.lg.carry = carry.data_ptr() if carry is not None else None
+        a.lg.ldc = ldc if carry is not None else k
+        a.lg.piece_len = self.sched.piece_len
+        a.n_owned_y = rp.n_owned
+        a.Ypart, a.ldp = self.Y_loc.data_ptr(), k
+        a.y_dst = self.y_dst.data_ptr()
+        a.parity_off_v = half // 16
+        a.cptr, a.cslot = self.cptr.data_ptr(), self.cslot.data_ptr()
+        a.slots, a.lds = self.slots.data_ptr(), k
+
+    def launch(self, Y: torch.Tensor, beta: float, phases=PH_ALL, new_epoch=True):
+        if new_epoch:
+            self.epoch += 1
+        a = self.args
+        a.Y, a.ldy, a.beta = Y.data_ptr(), Y.stride(0) if Y.shape[0] > 1 else self.k_loc, float(beta)
+        self._launch(native.cuda().sp3_fused_spmm_f32, phases)
+
+    def run(self, Y: torch.Tensor, beta: float = 0.0):
+        self.launch(Y, beta)
+        return Y
+
+
+def run_lockstep(fused_ops, launch_args=None):
+    """Runs one epoch of every given fused op (all ranks of a LocalFabric mesh,
+    on one GPU and one stream) phase by phase: START of every rank, then MAIN
+    of every rank, then FINISH of every rank.  No launch waits for a later
+    one."""
+    launch_args = launch_args or [()] * len(fused_ops)
+    for i, phase in enumerate((PH_START, PH_MAIN, PH_FINISH)):
+        for f, args in zip(fused_ops, launch_args):
+            f.launch(*args, phases=phase, new_epoch=(i == 0))

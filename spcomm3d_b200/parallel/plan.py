@@ -49,6 +49,7 @@ class SidePlan:
     send_counts: np.ndarray    # int64 [npeers] rows each peer needs from me
     send_idx: np.ndarray       # int64 [sum send_counts] my owned-local indices, peer by peer
     peer_owned: np.ndarray     # int64 [npeers] size of every peer's owned block
+    push_offset: np.ndarray = None  # int64 [npeers] where my rows start inside peer p's send list
 
     @property
     def n_owned(self) -> int:
@@ -108,10 +109,18 @@ def build_side(directory: Directory, side: str, x: int, y: int) -> SidePlan:
         send_parts.append(own_pos[sel])
         send_counts[p] = int(sel.sum())
     send_idx = np.concatenate(send_parts) if send_parts else np.zeros(0, np.int64)
+    # cnt[q, p] = rows owned by p that q needs; peer p's send list is ordered by q, so my segment in it
+    # starts after the segments of all q < me
+    line_owner = owner[in_line]
+    cnt = np.zeros((npeers, npeers), np.int64)
+    for q in range(npeers):
+        cnt[q] = np.bincount(line_owner[((lmask >> q) & 1).astype(bool)], minlength=npeers)
+        cnt[q, q] = 0
+    push_offset = cnt[:me].sum(axis=0)
     return SidePlan(side, npeers, me, owned_gids.astype(np.int64),
                     np.concatenate([owned_gids, need]).astype(np.int64), recv_counts,
                     pos[need].astype(np.int32), need_owner.astype(np.int32), send_counts,
-                    send_idx.astype(np.int64), np.asarray(counts, np.int64).copy())
+                    send_idx.astype(np.int64), np.asarray(counts, np.int64).copy(), push_offset)
 
 
 @dataclass
@@ -188,7 +197,7 @@ class RankPlan:
         for name in ("row", "col"):
             sp = getattr(self, name)
             for f in ("owned_gids", "local_gids", "recv_counts", "recv_src_idx", "recv_peer", "send_counts",
-                      "send_idx", "peer_owned"):
+                      "send_idx", "peer_owned", "push_offset"):
                 arrays[f"{name}.{f}"] = getattr(sp, f)
         hdr = np.array([self.mesh.X, self.mesh.Y, self.mesh.Z, *self.coords, self.nrows, self.ncols, self.gnnz,
                         self.row.npeers, self.row.me, self.col.npeers, self.col.me], np.int64)
@@ -203,7 +212,7 @@ class RankPlan:
         for name, npeers, me in (("row", int(h[9]), int(h[10])), ("col", int(h[11]), int(h[12]))):
             sides[name] = SidePlan(name, npeers, me, *(z[f"{name}.{f}"] for f in (
                 "owned_gids", "local_gids", "recv_counts", "recv_src_idx", "recv_peer", "send_counts",
-                "send_idx", "peer_owned")))
+                "send_idx", "peer_owned", "push_offset")))
         return RankPlan(mesh, (int(h[3]), int(h[4]), int(h[5])), int(h[6]), int(h[7]), str(z["name"]),
                         sides["row"], sides["col"], z["rowptr"], z["rowidx"], z["colidx"], z["vals"],
                         z["src_perm"], gnnz=int(h[8]))

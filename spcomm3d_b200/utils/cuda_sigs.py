@@ -18,4 +18,16 @@ CUDA_SIGS = {
     "sp3_cuda_remap": ("int", "i64 p p i64 p p p"),
     "sp3_cuda_invert_perm": ("int", "i64 p p p p"),
     "sp3_cuda_touch_masks": ("int", "i64 p p p p p p p"),
+    "sp3_fused_struct_sizes": ("int", "p p p"),
+    "sp3_fused_sddmm_f32": ("int", "p p"),
+    "sp3_fused_spmm_f32": ("int", "p p"),
+    "sp3_symm_alloc": ("int", "u64 p"),
+    "sp3_symm_free": ("int", "p"),
+    "sp3_ipc_get_handle": ("int", "p p"),
+    "sp3_ipc_open": ("int", "p p"),
+    "sp3_ipc_close": ("int", "p"),
+    "sp3_can_access_peer": ("int", "int int p"),
+    "sp3_cuda_error_string": ("s", "int"),
+    "sp3_cuda_wait_flag": ("int", "p int u64 p p"),
+    "sp3_cuda_signal_flags": ("int", "p int int int p"),
 }

@@ -141,9 +141,43 @@ def build_host(force=False, verbose=False) -> Path:
 
 
 def build_cuda(force=False, verbose=False) -> Path:
+    """Compiles every .cu of csrc/kernels for sm_100a (one nvcc process per
+    file, in parallel) and links them into libsp3cuda.so."""
     lib = LIBDIR / "libsp3cuda.so"
-    _build(lib, _sources("kernels", {".cu"}), _sources("kernels", {".cuh", ".h"}), cuda_build_cmd(),
-           force, verbose)
+    srcs = _sources("kernels", {".cu"})
+    hdrs = _sources("kernels", {".cuh", ".h"})
+    cmd = cuda_build_cmd()
+    LIBDIR.mkdir(exist_ok=True)
+    stamp_file = lib.with_suffix(".stamp")
+    want = _stamp(list(srcs) + list(hdrs), cmd)
+    if not force and lib.exists() and stamp_file.exists() and stamp_file.read_text() == want:
+        return lib
+    with open(LIBDIR / ".build.lock", "w") as lk:
+        fcntl.flock(lk, fcntl.LOCK_EX)
+        if not force and lib.exists() and stamp_file.exists() and stamp_file.read_text() == want:
+            return lib
+        if verbose:
+            print("[spcomm3d_b200] building", lib.name, file=sys.stderr)
+        objdir = LIBDIR / "obj"
+        objdir.mkdir(exist_ok=True)
+        compile_cmd = [c for c in cmd if c != "-shared"] + ["-c"]
+
+        def one(src):
+            obj = objdir / (src.stem + ".o")
+            res = subprocess.run(compile_cmd + ["-o", str(obj), str(src)], capture_output=True, text=True)
+            if res.returncode != 0:
+                raise NativeError(f"nvcc failed on {src.name}:\n{res.stdout}\n{res.stderr}")
+            return obj
+
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=len(srcs)) as ex:
+            objs = list(ex.map(one, srcs))
+        tmp = lib.with_suffix(f".tmp{os.getpid()}.so")
+        res = subprocess.run(cmd + ["-o", str(tmp)] + [str(o) for o in objs], capture_output=True, text=True)
+        if res.returncode != 0:
+            raise NativeError(f"link of {lib.name} failed:\n{res.stdout}\n{res.stderr}")
+        os.replace(tmp, lib)
+        stamp_file.write_text(want)
     return lib
 
 
