@@ -1,0 +1,119 @@
+"""Shared pieces of the command-line programs: option parsing in the style of
+the reference (`-k k1,k2 -c Z matrix.bin`, miniapp/bench_spmm.cpp:33-103),
+process-group start-up and plan construction.
+
+Run single-process (`python -m spcomm3d_b200.cli.bench_sddmm ...`) or under
+`torchrun --nproc-per-node N` (one rank per GPU with NCCL, or CPU ranks with
+gloo when no GPU is present / `--device cpu`).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import torch
+
+from ..parallel.mesh import Mesh3D, MeshGroups, dims_create
+from ..parallel.partition import Directory, distribute_from_file
+from ..parallel.plan import build_my_plan, build_rank_plan
+from ..utils import binfmt, generate
+
+NUM_ITER = 5  # iterations per instance, as miniapp/bench_spmm.cpp:22
+
+
+def base_parser(prog: str, description: str) -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog=prog, description=description)
+    ap.add_argument("matrix", nargs="?", help="matrix in .bin format (or .mtx); omit when --gen is given")
+    ap.add_argument("-k", dest="klist", default="32", help="comma separated list of inner dimensions")
+    ap.add_argument("-c", "-z", dest="Z", type=int, default=1, help="Z: number of layers the k dimension is split over")
+    ap.add_argument("-i", dest="iters", type=int, default=NUM_ITER, help="iterations per instance")
+    ap.add_argument("--mesh", default=None, help="XxYxZ; default: balanced X>=Y for the given Z")
+    ap.add_argument("--dtype", default=None, choices=["fp32", "fp64"])
+    ap.add_argument("--variant", default=None, help="comma list of sparse,sparseNRB,fused,dense")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--gen", default=None, help="synthetic matrix: uniform:M:N:deg | rmat:scale[:ef] | zipf:M:N[:a[:dmax]] | er:M:N:deg")
+    ap.add_argument("--device", default=None, choices=["cpu", "cuda"])
+    ap.add_argument("--policy", default="respect_comm", choices=["respect_comm", "random"])
+    ap.add_argument("--json", action="store_true", help="also print one JSON record per instance")
+    ap.add_argument("-v", dest="verbose", action="store_true")
+    return ap
+
+
+def klist(text: str):
+    return [int(t) for t in text.split(",") if t]
+
+
+class Runtime:
+    def __init__(self, args):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        want_cuda = args.device != "cpu" and torch.cuda.is_available()
+        if args.device == "cuda" and not torch.cuda.is_available():
+            raise SystemExit("--device cuda but no CUDA device is visible")
+        self.device = torch.device("cuda", local) if want_cuda else torch.device("cpu")
+        if want_cuda:
+            torch.cuda.set_device(self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl" if want_cuda else "gloo",
+                                    **({"device_id": self.device} if want_cuda else {}))
+        if args.mesh:
+            self.mesh = Mesh3D.parse(args.mesh)
+        else:
+            if self.world % args.Z:
+                raise SystemExit(f"-c {args.Z} does not divide {self.world} ranks")
+            self.mesh = Mesh3D(*dims_create(self.world, args.Z))
+        if self.mesh.size != self.world:
+            raise SystemExit(f"mesh {self.mesh} needs {self.mesh.size} ranks but {self.world} are running")
+        self.groups = MeshGroups.create(self.mesh) if self.world > 1 else None
+        self.dtype = {"fp32": torch.float32, "fp64": torch.float64, None:
+                      (torch.float32 if want_cuda else torch.float64)}[args.dtype]
+
+    def variants(self, args, default):
+        v = args.variant.split(",") if args.variant else list(default)
+        if self.device.type != "cuda" or self.dtype != torch.float32:
+            v = [x for x in v if x != "fused"]
+        return v
+
+    def load_plan(self, args):
+        """(plan, matrix name).  Generated matrices are built identically on
+        every rank (no communication); files go through the collective reader."""
+        if args.gen:
+            m = generate.from_spec(args.gen, seed=args.seed)
+            _, plan = build_my_plan(m, self.mesh, self.rank, seed=args.seed, policy=args.policy)
+            return plan
+        if not args.matrix:
+            raise SystemExit("give a matrix file or --gen")
+        path = args.matrix
+        if path.endswith(".mtx"):
+            m = binfmt.read_mtx(path)
+            _, plan = build_my_plan(m, self.mesh, self.rank, seed=args.seed, policy=args.policy)
+            return plan
+        if self.world == 1:
+            m = binfmt.read_bin(path)
+            _, plan = build_my_plan(m, self.mesh, 0, seed=args.seed, policy=args.policy)
+            return plan
+        _, _, gnnz = binfmt.read_bin_header(path)
+        block, directory = distribute_from_file(path, self.mesh, self.groups, seed=args.seed, policy=args.policy)
+        return build_rank_plan(block, directory, self.groups.coords, gnnz=gnnz)
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+
+    def finish(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+
+    def say(self, *a):
+        if self.rank == 0:
+            print(*a)
+            sys.stdout.flush()

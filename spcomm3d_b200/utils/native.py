@@ -67,7 +67,7 @@ HOST_SIGS = {
     "sp3_cpu_spmm_f64": ("int", "i64 p p p p i64 i64 f64 p i64"),
     "sp3_cpu_rows_f32": ("int", "int i64 p p i64 p i64 i64"),
     "sp3_cpu_rows_f64": ("int", "int i64 p p i64 p i64 i64"),
-    "sp3_serial_sim": ("int", "u64 p p u64 u64 u32 u32 u64 p"),
+    "sp3_serial_sim": ("int", "u64 p p u64 u64 u32 u32 u64 int int p"),
     "sp3_count_excess": ("int", "u64 p p u64 u64 u32 u32 u64 p"),
 }
 

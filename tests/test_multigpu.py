@@ -1,0 +1,69 @@
+"""One process per GPU (NCCL + CUDA IPC): fused kernels and the library-collective
+variants against the fp64 oracle on real peers.  NVLS is off in NCCL and the
+fused kernels use plain peer loads/stores."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from dist_utils import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _rank_main(rank, world, meshstr, gen, k, variants):
+    from spcomm3d_b200.models.dist_ops import DistSDDMM, DistSpMM
+    from spcomm3d_b200.ops import oracle
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups, split_k
+    from spcomm3d_b200.parallel.plan import build_my_plan
+    from spcomm3d_b200.parallel.symm import IpcFabric
+    from spcomm3d_b200.utils import generate
+    from spcomm3d_b200.utils.sparse import CooMatrix
+    mesh = Mesh3D.parse(meshstr)
+    groups = MeshGroups.create(mesh)
+    dev = torch.device("cuda", rank)
+    m = generate.from_spec(gen, seed=3)
+    _, plan = build_my_plan(m, mesh, rank, seed=3)
+    fabric = IpcFabric(device=dev)
+    for variant in variants:
+        kw = {"fabric": fabric, "timeout_s": 10.0} if variant == "fused" else {}
+        sd = DistSDDMM(plan, groups, k, torch.float32, dev, variant, **kw)
+        sp = DistSpMM(plan, groups, k, torch.float32, dev, variant, **kw)
+        for epoch in range(2):
+            A = generate.fill_rows(np.arange(m.nrows), k, 0, k, seed=5 + epoch, stream=1, dtype=np.float64)
+            B = generate.fill_rows(np.arange(m.ncols), k, 0, k, seed=5 + epoch, stream=2, dtype=np.float64)
+            sd.fill_owned(sd.A_owned, plan.row.owned_gids, seed=5 + epoch, stream=1)
+            sd.fill_owned(sd.B_owned, plan.col.owned_gids, seed=5 + epoch, stream=2)
+            sp.fill_owned(sp.X_owned, plan.col.owned_gids, seed=5 + epoch, stream=2)
+            sd.poison_unowned()
+            sp.poison_unowned()
+            c = sd.run()
+            y = sp.run()
+            off, ln = plan.owned_nnz_slice()
+            mine = CooMatrix(m.nrows, m.ncols, plan.global_rows()[off:off + ln], plan.global_cols()[off:off + ln],
+                             plan.vals[off:off + ln])
+            ref = oracle.sddmm_ref(mine, A, B)
+            assert c.shape[0] == ln
+            if ln:
+                err = (c.cpu().double() - ref).abs().max()
+                assert err <= 2e-5 * max(1.0, ref.abs().max()) * k ** 0.5, (variant, "sddmm", float(err))
+            ko, kw_ = split_k(k, mesh.Z, plan.coords[2])
+            yref = oracle.spmm_ref(m, B)[plan.row.owned_gids][:, ko:ko + kw_]
+            if yref.numel():
+                err = (y.cpu().double() - yref).abs().max()
+                assert err <= 2e-5 * max(1.0, yref.abs().max()) * 8, (variant, "spmm", float(err))
+    fabric.close()
+
+
+def _meshes(n):
+    return {2: ["2x1x1", "1x2x1", "1x1x2"], 4: ["2x2x1", "2x1x2"], 8: ["2x2x2", "4x2x1", "1x1x8"]}.get(n, [])
+
+
+def test_all_variants_on_real_peers():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    n = torch.cuda.device_count()
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    for meshstr in _meshes(n):
+        run_ranks(_rank_main, n, meshstr, "zipf:3000:4000:1.6:700", 64, ["fused", "sparseNRB", "sparse", "dense"],
+                  backend="nccl")

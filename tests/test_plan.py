@@ -1,0 +1,128 @@
+"""Plan properties on virtual meshes: ownership, exactness of the need lists
+(volume == brute-force need-set count), layouts, persistence."""
+import itertools
+
+import numpy as np
+import pytest
+
+from spcomm3d_b200.parallel.mesh import Mesh3D
+from spcomm3d_b200.parallel.partition import Directory
+from spcomm3d_b200.parallel.plan import RankPlan, build_all_plans
+from spcomm3d_b200.parallel import virtual
+from spcomm3d_b200.utils import generate
+from spcomm3d_b200.utils.sparse import CooMatrix
+
+
+def _factorizations(n):
+    return [(x, y, z) for x, y, z in itertools.product(range(1, n + 1), repeat=3) if x * y * z == n]
+
+
+def _matrices():
+    yield generate.fixed_degree(120, 90, 4, seed=1)
+    yield generate.zipf_rows(150, 400, alpha=1.5, dmax=200, seed=2)
+    # empty rows, empty columns, an empty block region
+    yield CooMatrix(40, 50, [0, 0, 3, 39, 17], [1, 49, 1, 0, 20], np.ones(5), name="tiny")
+    yield CooMatrix(30, 30, [], [], [], name="empty")
+
+
+@pytest.mark.parametrize("n", [1, 2, 4, 8])
+def test_plans_for_every_mesh_shape(n):
+    for m in _matrices():
+        for (X, Y, Z) in _factorizations(n):
+            mesh = Mesh3D(X, Y, Z)
+            d, plans = build_all_plans(m, mesh, seed=5)
+            d.check()
+            assert len(plans) == n
+            # every id has exactly one owner, inside its mesh line
+            assert int(d.row_counts.sum()) == m.nrows and int(d.col_counts.sum()) == m.ncols
+            total_nnz = 0
+            for r, p in plans.items():
+                p.validate()
+                x, y, z = p.coords
+                if z == 0:
+                    total_nnz += p.nnz
+                # brute force need sets from the block's own nonzeros
+                rows, cols = p.global_rows(), p.global_cols()
+                assert (d.rowmap[rows] == x).all() and (d.colmap[cols] == y).all()
+                for side, ids, owner in ((p.row, rows, d.row_owner), (p.col, cols, d.col_owner)):
+                    need = np.unique(ids)
+                    mine = need[owner[need] == side.me]
+                    other = need[owner[need] != side.me]
+                    assert set(mine) <= set(side.owned_gids)
+                    assert sorted(other) == sorted(side.local_gids[side.n_owned:])  # exactly the needed rows
+                    assert (np.diff(side.owned_gids) > 0).all()
+                    # needed rows grouped by ascending owner, ascending id inside a group
+                    off = side.recv_offsets()
+                    for q in range(side.npeers):
+                        seg = side.local_gids[side.n_owned + off[q]: side.n_owned + off[q + 1]]
+                        assert (owner[seg] == q).all() and (np.diff(seg) > 0).all()
+            assert total_nnz == m.nnz
+            # send lists mirror receive lists
+            for r, p in plans.items():
+                x, y, z = p.coords
+                for q in range(mesh.Y):
+                    if q != y:
+                        other = plans[mesh.rank_of(x, q, z)]
+                        assert other.row.send_counts[y] == p.row.recv_counts[q]
+                for q in range(mesh.X):
+                    if q != x:
+                        other = plans[mesh.rank_of(q, y, z)]
+                        assert other.col.send_counts[x] == p.col.recv_counts[q]
+
+
+def test_respect_comm_never_moves_more_than_random_ownership():
+    m = generate.fixed_degree(2000, 2000, 5, seed=3)
+    mesh = Mesh3D(4, 4, 1)
+    _, a = build_all_plans(m, mesh, seed=1, policy="respect_comm")
+    _, b = build_all_plans(m, mesh, seed=1, policy="random")
+    va = sum(p.expand_rows()[1] for p in a.values())
+    vb = sum(p.expand_rows()[1] for p in b.values())
+    assert va < vb
+
+
+def test_sparse_volume_not_above_dense_volume_and_sim_agrees():
+    m = generate.fixed_degree(3000, 2500, 6, seed=4)
+    mesh = Mesh3D(4, 2, 1)
+    _, plans = build_all_plans(m, mesh, seed=9)
+    sim = virtual.serial_sim(m, 4, 2, seed=9)
+    recv = [p.expand_rows()[1] for p in plans.values()]
+    send = [p.expand_rows()[0] for p in plans.values()]
+    assert np.isclose(sim["sparse"]["avgRecvVol"], np.mean(recv)) and sim["sparse"]["maxRecvVol"] == max(recv)
+    assert np.isclose(sim["sparse"]["avgSendVol"], np.mean(send)) and sim["sparse"]["maxSendVol"] == max(send)
+    assert sim["sparse"]["avgRecvVol"] <= sim["dense"]["avgRecvVol"]
+    ex = virtual.count_excess(m, 4, 2, seed=9)
+    assert ex["excess_rows"] >= 0 and ex["stored_rows"] == 2 * (m.nrows * 2 + m.ncols * 4) / 2
+
+
+def test_large_virtual_mesh_simulation():
+    m = CooMatrix.random_unique(5000, 5000, 25000, seed=1)
+    X, Y = virtual.find_xy(1024)
+    assert (X, Y) == (32, 32)
+    s = virtual.serial_sim(m, 181, 181, seed=2, policy="random", mode="spmm_pre")
+    assert s["sparse"]["avgRecvVol"] <= s["dense"]["avgRecvVol"]
+    assert virtual.count_empty(m)[0] > 0
+
+
+def test_plan_save_load(tmp_path):
+    m = generate.fixed_degree(200, 150, 5, seed=1)
+    _, plans = build_all_plans(m, Mesh3D(2, 2, 2), seed=2)
+    p = plans[5]
+    path = str(tmp_path / "plan5")
+    p.save(path)
+    q = RankPlan.load(path)
+    assert q.coords == p.coords and str(q.mesh) == "2x2x2" and q.gnnz == p.gnnz and q.name == p.name
+    for f in ("rowptr", "rowidx", "colidx", "vals", "src_perm"):
+        assert np.array_equal(getattr(p, f), getattr(q, f))
+    for side in ("row", "col"):
+        for f in ("owned_gids", "local_gids", "recv_counts", "recv_src_idx", "send_idx", "push_offset"):
+            assert np.array_equal(getattr(getattr(p, side), f), getattr(getattr(q, side), f))
+
+
+def test_directory_is_deterministic_and_seeded():
+    m = generate.fixed_degree(300, 300, 4, seed=1)
+    a = Directory.from_global(m, Mesh3D(2, 2, 1), seed=3)
+    b = Directory.from_global(m, Mesh3D(2, 2, 1), seed=3)
+    c = Directory.from_global(m, Mesh3D(2, 2, 1), seed=4)
+    assert np.array_equal(a.rowmap, b.rowmap) and np.array_equal(a.row_owner, b.row_owner)
+    assert not np.array_equal(a.rowmap, c.rowmap)
+    assert np.array_equal(a.rpvec() // 2, a.rowmap)  # owner's mesh row is the row's mesh row

@@ -1,0 +1,156 @@
+"""Stats line format, CLI programs under torchrun (gloo), host-side failure detection."""
+import datetime
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from dist_utils import ROOT, free_port, run_ranks
+from spcomm3d_b200.utils import binfmt, generate, stats
+
+ENV = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
+
+
+def test_stats_line_roundtrip_and_reference_layout():
+    agg = {"avg": [1.5, 2048.0, 1.5, 2000.25], "max": [2, 4096, 2, 4000], "times": [1.0, 2.0, 0.5, 3.0, 6.0]}
+    line = stats.format_line("web", "sparse sddmm PRE", 8, 128, 2, agg)
+    assert len(line.split()) == 2 + 2 + 16  # name, 3-word alg, 16 numeric fields
+    p = stats.parse_line(line)
+    assert p["alg"] == "sparse sddmm PRE" and p["P"] == 8 and p["k"] == 128 and p["Z"] == 2
+    assert p["max"] == [2, 4096, 2, 4000] and p["times"]["total"] == 6.0
+    # a line as the reference prints it (integer milliseconds)
+    ref = "web sparseNB sddmm POST 8 128 2 1.00 10.00 1.00 5.00 1 10 1 5 3 1 0 7 11"
+    q = stats.parse_line(ref)
+    assert q["alg"] == "sparseNB sddmm POST" and q["times"]["comp"] == 7.0
+
+
+def test_roofline_picks_the_slowest_resource():
+    r = stats.roofline(flops=2e9, nvlink_bytes_per_rank=0.5e9, hbm_bytes_per_rank=1e9, ms=1.0)
+    assert r["bound"] == "nvlink" and abs(r["nvlink_ms"] - 0.5e9 / 770e9 * 1e3) < 1e-9 and 0 < r["fraction"] < 1
+
+
+def _torchrun(n, module, *args):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()), "-m", module, *args]
+    return subprocess.run(cmd, capture_output=True, text=True, env=ENV, timeout=300, cwd=ROOT)
+
+
+def test_bench_cli_under_torchrun_prints_parsable_lines(tmp_path):
+    m = generate.fixed_degree(400, 300, 5, seed=1)
+    path = str(tmp_path / "web.bin")
+    binfmt.write_bin(path, m)
+    out = _torchrun(4, "spcomm3d_b200.cli.bench_sddmm", "-k", "8,16", "-c", "2", "-i", "2", "--device", "cpu", path)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("web ")]
+    # 2 k values x 3 CPU variants x 2 iterations x 2 phases
+    assert len(lines) == 2 * 3 * 2 * 2
+    algs = {stats.parse_line(l)["alg"] for l in lines}
+    assert algs == {f"{v} sddmm {p}" for v in ("sparse", "sparseNRB", "dense") for p in ("PRE", "POST")}
+    pre = [stats.parse_line(l) for l in lines if "sparseNRB sddmm PRE" in l and " 16 2 " in l][0]
+    assert pre["P"] == 4 and pre["avg"][1] == pre["avg"][3]  # everything sent is received
+    dense = [stats.parse_line(l) for l in lines if "dense sddmm PRE" in l and " 16 2 " in l][0]
+    assert dense["avg"][3] >= pre["avg"][3]
+    out = _torchrun(2, "spcomm3d_b200.cli.bench_spmm", "-k", "8", "-c", "1", "-i", "1", "--device", "cpu", path)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert sum(l.startswith("web ") for l in out.stdout.splitlines()) == 3 * 2
+
+
+def test_checksum_tools_agree(tmp_path):
+    from spcomm3d_b200.cli import num_check_seq
+    m = generate.fixed_degree(300, 300, 4, seed=2)
+    mtx, binp = str(tmp_path / "c.mtx"), str(tmp_path / "c.bin")
+    binfmt.write_mtx(mtx, m)
+    binfmt.conv2bin(mtx, binp)
+    serial = num_check_seq.checksum_of(mtx, 8)
+    # definition check against the plain formula
+    ref = sum(v * 8 * (r / 1000.0) * (c / 1000.0) for r, c, v in zip(m.rows, m.cols, m.vals))
+    assert abs(serial - ref) < 1e-9 * max(1.0, abs(ref))
+    out = _torchrun(4, "spcomm3d_b200.cli.num_res_check", "-k", "8", "-c", "2", "--device", "cpu", binp)
+    assert out.returncode == 0, out.stderr[-2000:]
+    sums = [float(l.rsplit("=", 1)[1]) for l in out.stdout.splitlines() if l.startswith("Global numerical sum") and "sddmm" in l]
+    assert len(sums) == 2 and all(abs(s - serial) < 1e-6 * max(1.0, abs(serial)) for s in sums)
+
+
+def test_single_process_tools(tmp_path):
+    from spcomm3d_b200.cli import count_excess, read_distribute, serial_sim
+    m = generate.fixed_degree(200, 200, 3, seed=2)
+    p = str(tmp_path / "g.bin")
+    binfmt.write_bin(p, m)
+    serial_sim.main(["-n", "4,16", "-m", p])
+    count_excess.main([p, "-n", "16"])
+    count_excess.main([p, "--empty"])
+    read_distribute.main([p, "-x", "2", "-y", "2", "-o", str(tmp_path / "blk")])
+    total = sum(binfmt.read_bin_header(str(tmp_path / f"blk_{x}_{y}.bin"))[2] for x in range(2) for y in range(2))
+    assert total == m.nnz
+
+
+# ---- failure detection, all on the host -------------------------------------
+def _absent_peer(rank, world):
+    """Rank 1 never joins the exchange; rank 0's collective must end with an
+    error after the group's timeout instead of hanging."""
+    import torch.distributed as dist
+    from spcomm3d_b200.models.dist_ops import DistSpMM
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups
+    from spcomm3d_b200.parallel.plan import build_my_plan
+    mesh = Mesh3D(2, 1, 1)
+    groups = MeshGroups.create(mesh)
+    m = generate.fixed_degree(100, 100, 3, seed=1)
+    _, plan = build_my_plan(m, mesh, rank, seed=1)
+    op = DistSpMM(plan, groups, 8, torch.float64, "cpu", "sparseNRB")
+    op.run()  # one healthy step
+    if rank == 1:
+        return  # leaves between steps
+    with pytest.raises(Exception):
+        op.run()
+
+
+def _entry_short_timeout(rank, world, port, fn):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    fn(rank, world)
+
+
+def test_absent_peer_ends_in_an_error_not_a_hang():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    port = free_port()
+    procs = [ctx.Process(target=_entry_short_timeout, args=(r, 2, port, _absent_peer)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(not p.is_alive() for p in procs)
+    assert procs[0].exitcode == 0, "rank 0 should have caught the timeout error"
+
+
+def _heartbeat_and_fingerprint(rank, world):
+    from spcomm3d_b200.parallel import health
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups
+    from spcomm3d_b200.parallel.plan import build_my_plan
+    mesh = Mesh3D(2, 1, 1)
+    groups = MeshGroups.create(mesh)
+    m = generate.fixed_degree(100, 100, 3, seed=1)
+    _, plan = build_my_plan(m, mesh, rank, seed=1)
+    health.check_consistent(plan, groups)
+    # rank 1 plans a different matrix: everyone must be told
+    _, wrong = build_my_plan(generate.fixed_degree(100, 100, 4, seed=1) if rank == 1 else m, mesh, rank, seed=1)
+    with pytest.raises(ValueError, match="not consistent"):
+        health.check_consistent(wrong, groups)
+    hb = health.Heartbeat(rank, world)
+    import torch.distributed as dist
+    dist.barrier()
+    hb.beat(1)
+    hb.require_alive(1, wait_s=10)
+    if rank == 0:
+        hb.beat(2)
+        with pytest.raises(health.RankFailure, match=r"\[1\]"):
+            hb.require_alive(2, wait_s=0.5)  # rank 1 never reports step 2
+
+
+def test_plan_fingerprint_and_heartbeat():
+    run_ranks(_heartbeat_and_fingerprint, 2)
