@@ -67,7 +67,13 @@ struct FusedComm {
     const int* push_to;      // ranks I push partial results to
     const int* contrib;      // ranks that push partial results to me
     int n_read, n_readers, n_push, n_contrib;
+    unsigned long long* stamps;  // optional [4]: globaltimer at kernel start, last pull done, MAIN done, FINISH done
 };
+
+enum Stamp : int { T_START = 0, T_PULLED = 1, T_MAIN = 2, T_FINISH = 3 };
+__device__ __forceinline__ void stamp(const FusedComm& c, int which) {
+    if (c.stamps) c.stamps[which] = globaltimer_ns();
+}
 
 __device__ __forceinline__ int warp_ticket(int* ctr, int lane) {
     int t = 0;
@@ -128,6 +134,7 @@ __device__ __forceinline__ bool wait_counter(const FusedComm& c, int which, int 
 }
 
 __device__ __forceinline__ void start_phase(const FusedComm& c) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamp(c, T_START);
     if (blockIdx.x == 0 && threadIdx.x < c.n_readers) {
         __threadfence_system();
         signal(c, F_READY, c.readers[threadIdx.x]);
@@ -171,6 +178,7 @@ __device__ __forceinline__ void main_epilogue(const FusedComm& c, int lane, int 
         __threadfence_system();
         for (int i = lane; i < c.n_read; i += 32) signal(c, F_DONE, c.read_from[i]);
         for (int i = lane; i < c.n_push; i += 32) signal(c, F_PART, c.push_to[i]);
+        if (lane == 0) stamp(c, T_MAIN);
     }
 }
 
@@ -181,7 +189,10 @@ __device__ __forceinline__ void finish_epilogue(const FusedComm& c, int lane, in
     int old = 0;
     if (lane == 0) old = atomicAdd(c.ctrl + C_FIN_DONE, 1);
     old = __shfl_sync(0xffffffffu, old, 0);
-    if (old == nwarps - 1 && lane == 0) wait_all(c, F_DONE, c.readers, c.n_readers, W_DONE);
+    if (old == nwarps - 1 && lane == 0) {
+        wait_all(c, F_DONE, c.readers, c.n_readers, W_DONE);
+        stamp(c, T_FINISH);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -252,7 +263,7 @@ __global__ void __launch_bounds__(256) fused_sddmm_kernel(const FusedSddmmArgs a
                 pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) atomicAdd(c.ctrl + C_PULLS_DONE, 1);
+                if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
             } else {
                 if (!pulled) {
                     ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
@@ -354,7 +365,7 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
                 pull_rows(r0, r1, a.x_src, Xv + (long long)a.n_owned_x * ldx_v, ldx_v, a.nvec, lane);
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) atomicAdd(c.ctrl + C_PULLS_DONE, 1);
+                if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
             } else {
                 if (!pulled) {
                     ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);

@@ -269,7 +269,7 @@ class DistSpMM(_Dist3DOp):
             pre = self._dense_col.stats_gather()
             mo = self._dense_row.max_owned
             allv = int(p.row.peer_owned.sum()) * k
-            post = ((1, allv), (1, int(p.row.peer_owned[p.row.me]) * k))
+            post = ((1, allv), (1, int(p.row.peer_owned[p.row.me]) * k)) if p.row.npeers > 1 else ((0, 0), (0, 0))
         else:
             s, r, sm, rm = p.expand_rows(("col",))
             pre = ((sm, s * k), (rm, r * k))

@@ -35,7 +35,7 @@ class _Comm(C.Structure):
     _fields_ = [("me", C.c_int), ("epoch", C.c_int), ("phases", C.c_int), ("timeout_ns", C.c_ulonglong),
                 ("status", P), ("ctrl", P), ("pad", P), ("peer_pad", P), ("read_from", P), ("readers", P),
                 ("push_to", P), ("contrib", P), ("n_read", C.c_int), ("n_readers", C.c_int),
-                ("n_push", C.c_int), ("n_contrib", C.c_int)]
+                ("n_push", C.c_int), ("n_contrib", C.c_int), ("stamps", P)]
 
 
 class _SddmmArgs(C.Structure):
@@ -141,6 +141,8 @@ class _FusedBase:
         comm.ctrl = self.ctrl.data_ptr()
         comm.pad = self.pad.data_ptr()
         comm.peer_pad = self.peer_pad.data_ptr()
+        self.stamps = torch.zeros(4, dtype=torch.int64, device=self.device)
+        comm.stamps = self.stamps.data_ptr()
 
     def _side_tables(self, side, region):
         """(addresses of every local row in its owner's heap, addresses of the rows to pull)."""
@@ -164,6 +166,15 @@ class _FusedBase:
             what = {1: "bad index", 2: "wait timed out"}.get(st[0], f"code {st[0]}")
             raise FusedStatusError(f"fused kernel on rank {self.rank}: {what} at {_SITES.get(st[1], st[1])}, "
                                    f"peer/slot {st[2]}, observed {st[3]} (epoch {self.epoch})")
+
+    def phase_ms(self) -> dict:
+        """Device timestamps of the last launch (synchronises): time from kernel
+        start until all remote rows were pulled, until MAIN finished (compute
+        done, partial results pushed and signalled) and until the kernel's
+        final handshake."""
+        torch.cuda.synchronize(self.device)
+        t = self.stamps.tolist()
+        return {"pull": max(0, t[1] - t[0]) / 1e6, "main": (t[2] - t[0]) / 1e6, "total": (t[3] - t[0]) / 1e6}
 
     def _launch(self, fn, phases):
         self.args.comm.phases = phases

@@ -183,6 +183,8 @@ class DenseExchange:
     def stats_gather(self):
         # bcast model of src/comm_stats.cpp:107-120: own block out once, all other blocks in
         s = self.side
+        if s.npeers == 1:
+            return (0, 0), (0, 0)
         mine = int(s.peer_owned[s.me]) * self.k
         allv = int(s.peer_owned.sum()) * self.k
         return (1, mine), (s.npeers, allv - mine)
