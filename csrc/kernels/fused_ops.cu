@@ -45,7 +45,7 @@ namespace sp3 {
 
 constexpr int MAX_RANKS = 64;
 enum FlagKind : int { F_READY = 0, F_DONE = 1, F_PART = 2, F_KINDS = 3 };
-enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_WORDS = 8 };
+enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_TICKET_WORK = 6, C_WORDS = 8 };
 enum Phase : int { PH_START = 1, PH_MAIN = 2, PH_FINISH = 4 };
 enum WaitSite : int { W_READY = 1, W_PULLS = 2, W_PART = 3, W_DONE = 4 };
 
@@ -75,11 +75,17 @@ __device__ __forceinline__ void stamp(const FusedComm& c, int which) {
     if (c.stamps) c.stamps[which] = globaltimer_ns();
 }
 
-__device__ __forceinline__ int warp_ticket(int* ctr, int lane) {
+// Work is handed out by one counter; a ticket covers `n` consecutive work
+// items so that the counter sees a few ten-thousand atomics per launch instead
+// of one per item (atomics on one address serialise in L2).
+__device__ __forceinline__ int warp_ticket(int* ctr, int lane, int n = 1) {
     int t = 0;
-    if (lane == 0) t = atomicAdd(ctr, 1);
+    if (lane == 0) t = atomicAdd(ctr, n);
     return __shfl_sync(0xffffffffu, t, 0);
 }
+
+constexpr int SDDMM_UNITS_PER_TICKET = 8;
+constexpr int SPMM_ITEMS_PER_TICKET = 4;
 
 __device__ __forceinline__ bool aborted(const FusedComm& c) {
     return *reinterpret_cast<volatile int*>(c.ctrl + C_ABORT) != 0;
@@ -204,7 +210,9 @@ struct FusedSddmmArgs {
     const int* rowidx;
     const int* colidx;
     const float* sval;
-    const float4* const* a_rows;  // [rows of the local A layout] absolute row addresses
+    const int* a_refs;            // [rows of the local A layout] owner rank << 25 | row in the owner's block
+    const unsigned long long* a_bases;  // [world] address of every rank's A block as mapped here
+    int world;
     float* B_loc;                 // local B block [owned | pulled]
     long long ldb;
     int n_owned_b, n_recv_b;
@@ -236,11 +244,14 @@ struct StoreSlices {
 };
 
 template <int G, int R, int U>
-__global__ void __launch_bounds__(256) fused_sddmm_kernel(const FusedSddmmArgs a) {
+__global__ void __launch_bounds__(256, SP3_SDDMM_MINB) fused_sddmm_kernel(const FusedSddmmArgs a) {
     const FusedComm& c = a.comm;
     const int lane = threadIdx.x & 31;
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
+    __shared__ unsigned long long a_bases[MAX_RANKS];
+    if (threadIdx.x < MAX_RANKS) a_bases[threadIdx.x] = threadIdx.x < a.world ? a.a_bases[threadIdx.x] : 0ull;
+    __syncthreads();
     if (c.phases & PH_START) start_phase(c);
     if (c.phases & PH_MAIN) {
         bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
@@ -248,30 +259,33 @@ __global__ void __launch_bounds__(256) fused_sddmm_kernel(const FusedSddmmArgs a
         const int n_pull = (a.n_recv_b + PULL_ROWS - 1) / PULL_ROWS;
         const long long per_unit = (long long)SLOTS * SDDMM_PER_SLOT;
         const long long n_units = (a.nnz + per_unit - 1) / per_unit;
-        const long long total = n_pull + n_units;
-        const RowsByPointer<float> arows{a.a_rows};
+        const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull};
         const StoreSlices store{a.sval, a.out, a.zbuf, a.Z, a.my_z, parity, a.zbase, a.zrem, a.zwidth};
         float4* Bv = reinterpret_cast<float4*>(a.B_loc);
         const long long ldb_v = a.ldb / 4;
         bool pulled = n_pull == 0;
+        // pull tickets first (one tile each), then compute tickets (several units each)
         while (ok) {
-            const long long t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
-            if (t >= total) break;
-            if (t < n_pull) {
-                const int r0 = (int)t * PULL_ROWS;
-                const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
-                pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
-                __threadfence();
-                __syncwarp();
-                if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
-            } else {
-                if (!pulled) {
-                    ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
-                    pulled = true;
-                    if (!ok) break;
-                }
-                sddmm_warp_unit<float, G, R, U>(t - n_pull, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
+            const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
+            if (t >= n_pull) break;
+            const int r0 = t * PULL_ROWS;
+            const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
+            pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
+            __threadfence();
+            __syncwarp();
+            if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
+        }
+        while (ok) {
+            const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
+            if (u0 >= n_units) break;
+            if (!pulled) {
+                ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
+                pulled = true;
+                if (!ok) break;
             }
+            const long long u1 = u0 + SDDMM_UNITS_PER_TICKET < n_units ? u0 + SDDMM_UNITS_PER_TICKET : n_units;
+            for (long long u = u0; u < u1; ++u)
+                sddmm_warp_unit<float, G, R, U>(u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
         }
         main_epilogue(c, lane, nwarps);
     }
@@ -350,7 +364,6 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
     if (c.phases & PH_MAIN) {
         bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
         const int n_pull = (a.n_recv_x + PULL_ROWS - 1) / PULL_ROWS;
-        const int total = n_pull + a.nitems;
         float4* Xv = reinterpret_cast<float4*>(a.X_loc);
         const long long ldx_v = a.ldx / 4;
         const EmitOwnedOrPush emit{reinterpret_cast<float4*>(a.Ypart), a.ldp / 4, a.n_owned_y, a.y_dst,
@@ -358,23 +371,26 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
         bool pulled = n_pull == 0;
         while (ok) {
             const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
-            if (t >= total) break;
-            if (t < n_pull) {
-                const int r0 = t * PULL_ROWS;
-                const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
-                pull_rows(r0, r1, a.x_src, Xv + (long long)a.n_owned_x * ldx_v, ldx_v, a.nvec, lane);
-                __threadfence();
-                __syncwarp();
-                if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
-            } else {
-                if (!pulled) {
-                    ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
-                    pulled = true;
-                    if (!ok) break;
-                }
-                spmm_warp_item<float, G, R, U>(__ldg(a.items + (t - n_pull)), a.rowptr, a.colidx, a.val, Xv, ldx_v,
-                                               a.nvec, emit, a.lg, lane);
+            if (t >= n_pull) break;
+            const int r0 = t * PULL_ROWS;
+            const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
+            pull_rows(r0, r1, a.x_src, Xv + (long long)a.n_owned_x * ldx_v, ldx_v, a.nvec, lane);
+            __threadfence();
+            __syncwarp();
+            if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
+        }
+        while (ok) {
+            const int i0 = warp_ticket(c.ctrl + C_TICKET_WORK, lane, SPMM_ITEMS_PER_TICKET);
+            if (i0 >= a.nitems) break;
+            if (!pulled) {
+                ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
+                pulled = true;
+                if (!ok) break;
             }
+            const int i1 = i0 + SPMM_ITEMS_PER_TICKET < a.nitems ? i0 + SPMM_ITEMS_PER_TICKET : a.nitems;
+            for (int it = i0; it < i1; ++it)
+                spmm_warp_item<float, G, R, U>(__ldg(a.items + it), a.rowptr, a.colidx, a.val, Xv, ldx_v, a.nvec, emit,
+                                               a.lg, lane);
         }
         main_epilogue(c, lane, nwarps);
     }

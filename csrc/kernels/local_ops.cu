@@ -24,7 +24,7 @@ namespace sp3 {
 // warps stride over work units (see sddmm_warp_unit).
 // ---------------------------------------------------------------------------
 template <typename T, int G, int R, int U>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, SP3_SDDMM_MINB)
 sddmm_vec_kernel(long long nnz, const int* __restrict__ rowidx, const int* __restrict__ colidx,
                  const T* __restrict__ sval, const T* __restrict__ A, long long lda,
                  const T* __restrict__ B, long long ldb, int nvec, T* __restrict__ out) {
@@ -65,6 +65,11 @@ sddmm_scalar_kernel(long long nnz, const int* __restrict__ rowidx, const int* __
 // Rows without nonzeros are covered by rows items, so beta is applied to
 // every row exactly once.
 // ---------------------------------------------------------------------------
+#ifndef SP3_SPMM_ITEMS_PER_STEP
+#define SP3_SPMM_ITEMS_PER_STEP 4
+#endif
+constexpr int SPMM_ITEMS_PER_STEP = SP3_SPMM_ITEMS_PER_STEP;
+
 template <typename T, int G, int R, int U>
 __global__ void __launch_bounds__(256)
 spmm_items_kernel(int nitems, const int4* __restrict__ items, const long long* __restrict__ rowptr,
@@ -75,6 +80,20 @@ spmm_items_kernel(int nitems, const int4* __restrict__ items, const long long* _
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int lane = threadIdx.x & 31;
     const EmitLocal<T> emit{reinterpret_cast<V*>(Y), ldy / Vec<T>::N, beta};
+    if (lg.ticket) {
+        // dynamic hand-out, SPMM_ITEMS_PER_STEP items per ticket: rows of a power-law matrix differ too much in
+        // cost for a fixed assignment to balance
+        for (;;) {
+            int base = 0;
+            if (lane == 0) base = atomicAdd(lg.ticket, SPMM_ITEMS_PER_STEP);
+            base = __shfl_sync(0xffffffffu, base, 0);
+            if (base >= nitems) break;
+            for (int it = base; it < base + SPMM_ITEMS_PER_STEP && it < nitems; ++it)
+                spmm_warp_item<T, G, R, U>(__ldg(items + it), rowptr, colidx, val, reinterpret_cast<const V*>(X),
+                                           ldx / Vec<T>::N, nvec, emit, lg, lane);
+        }
+        return;
+    }
     for (int it = warp0; it < nitems; it += nwarps)
         spmm_warp_item<T, G, R, U>(__ldg(items + it), rowptr, colidx, val, reinterpret_cast<const V*>(X),
                                    ldx / Vec<T>::N, nvec, emit, lg, lane);
@@ -261,6 +280,10 @@ int launch_spmm(int nrows, int nitems, const int4* items, const long long* rowpt
     }
     int G, R;
     pick_shape(nvec, &G, &R, true);
+    if (lg.ticket) {
+        cudaError_t e = cudaMemsetAsync(lg.ticket, 0, sizeof(int), st);
+        if (e != cudaSuccess) return (int)e;
+    }
     const long long needed = ((long long)nitems + 7) / 8;
 #define SP3_SPMM(GG, RR)                                                                                       \
     spmm_items_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>                                                            \
@@ -304,16 +327,16 @@ SP3_API int sp3_cuda_sddmm_f64(long long nnz, const int* ri, const int* ci, cons
 SP3_API int sp3_cuda_spmm_f32(int nrows, int nitems, const void* items, const long long* rowptr, const int* ci,
                               const float* val, const float* X, long long ldx, int k, float beta, float* Y,
                               long long ldy, const int* first_piece, const int* npieces, int* counters,
-                              void* carry, long long ldc, int piece_len, void* stream) {
-    SpmmLong lg{first_piece, npieces, counters, carry, ldc, piece_len};
+                              void* carry, long long ldc, int piece_len, int* ticket, void* stream) {
+    SpmmLong lg{first_piece, npieces, counters, carry, ldc, piece_len, ticket};
     return launch_spmm<float>(nrows, nitems, (const int4*)items, rowptr, ci, val, X, ldx, k, beta, Y, ldy, lg,
                               (cudaStream_t)stream);
 }
 SP3_API int sp3_cuda_spmm_f64(int nrows, int nitems, const void* items, const long long* rowptr, const int* ci,
                               const double* val, const double* X, long long ldx, int k, double beta, double* Y,
                               long long ldy, const int* first_piece, const int* npieces, int* counters,
-                              void* carry, long long ldc, int piece_len, void* stream) {
-    SpmmLong lg{first_piece, npieces, counters, carry, ldc, piece_len};
+                              void* carry, long long ldc, int piece_len, int* ticket, void* stream) {
+    SpmmLong lg{first_piece, npieces, counters, carry, ldc, piece_len, ticket};
     return launch_spmm<double>(nrows, nitems, (const int4*)items, rowptr, ci, val, X, ldx, k, beta, Y, ldy, lg,
                                (cudaStream_t)stream);
 }
@@ -422,7 +445,7 @@ SP3_API int sp3_cuda_spmm_f32_noalloc(int nrows, int nitems, const void* items, 
         err = cudaMemsetAsync(base, 0, (size_t)nlong * sizeof(int), st);
         if (err != cudaSuccess) return (int)err;
     }
-    sp3::SpmmLong lg{first_piece, npieces, (int*)base, (void*)(base + counters_bytes), ldc, piece_len};
+    sp3::SpmmLong lg{first_piece, npieces, (int*)base, (void*)(base + counters_bytes), ldc, piece_len, nullptr};
     return sp3::launch_spmm<float>(nrows, nitems, (const int4*)items, rowptr, colidx, val, X, ldx, k, beta, Y, ldy,
                                    lg, st);
 }

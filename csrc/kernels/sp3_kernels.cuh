@@ -3,8 +3,8 @@
 // (fused_ops.cu).  Where dense rows come from and where results go is a
 // template policy, so both families run the same inner loops:
 //
-//   SDDMM   A rows:  RowsByStride (one local block) | RowsByPointer (a table of
-//                    absolute row addresses, some of them in peers' memory)
+//   SDDMM   A rows:  RowsByStride (one local block) | RowsByPeerRef (rows that
+//                    stay in their owners' memory, local or peer)
 //           output:  StoreLocal | the fused kernel's slice-routing store
 //   SpMM    emit:    EmitLocal (Y = beta*Y + acc) | the fused kernel's
 //                    owned-or-push emit
@@ -16,6 +16,16 @@
 namespace sp3 {
 
 constexpr int SDDMM_PER_SLOT = 32;  // nonzeros per lane group; multiple of every G
+
+// Tuning knobs (compile time): resident 256-thread blocks per SM the SDDMM
+// kernels are compiled for, and whether the loop over the sub-batches of an
+// index batch is unrolled (more loads in flight per warp, more registers).
+#ifndef SP3_SDDMM_MINB
+#define SP3_SDDMM_MINB 4
+#endif
+#ifndef SP3_SDDMM_UNROLL_BATCH
+#define SP3_SDDMM_UNROLL_BATCH 1
+#endif
 
 template <int G> __device__ __forceinline__ unsigned group_mask(int slot) {
     return G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (slot * G));
@@ -50,16 +60,33 @@ __device__ __forceinline__ void group_transpose_reduce(T (&v)[N], unsigned gmask
 }
 
 // ---- row access policies ---------------------------------------------------
+// A policy turns the local row index of a nonzero into a 31-bit *reference*
+// (`ref`, evaluated by every lane for its own nonzero when a batch of indices
+// is read, so a table lookup is off the critical path) and a reference into
+// the address of the dense row (`resolve`, pure arithmetic).  The reference is
+// what the lane group passes round by shuffle and compares to detect a row
+// change.
 template <typename T> struct RowsByStride {
     using V = typename Vec<T>::type;
     const V* base;
     long long ld_v;
-    __device__ __forceinline__ const V* row(int l) const { return base + (long long)l * ld_v; }
+    __device__ __forceinline__ int ref(int row) const { return row; }
+    __device__ __forceinline__ const V* resolve(int r) const { return base + (long long)r * ld_v; }
 };
-template <typename T> struct RowsByPointer {
+// Rows that live in the owners' heaps: reference = owner rank (6 bits) and row
+// number inside the owner's block (25 bits); `bases` (shared memory) holds the
+// block address of every rank as mapped into this process.
+constexpr int PEER_REF_SHIFT = 25;
+template <typename T> struct RowsByPeerRef {
     using V = typename Vec<T>::type;
-    const V* const* table;  // table[l] = address of local row l (may be peer memory)
-    __device__ __forceinline__ const V* row(int l) const { return ldg_ptr(table + l); }
+    const int* table;                  // [local rows] references
+    const unsigned long long* bases;   // [ranks] block base addresses
+    unsigned long long row_bytes;
+    __device__ __forceinline__ int ref(int row) const { return __ldg(table + row); }
+    __device__ __forceinline__ const V* resolve(int r) const {
+        return reinterpret_cast<const V*>(bases[r >> PEER_REF_SHIFT] +
+                                          (unsigned long long)(r & ((1 << PEER_REF_SHIFT) - 1)) * row_bytes);
+    }
 };
 
 template <typename T> struct StoreLocal {
@@ -76,7 +103,7 @@ template <typename T> struct StoreLocal {
 // A group reads its (row, col) pairs G at a time with one coalesced load per
 // array and hands them round with in-group shuffles; each lane holds R
 // 16-byte vectors of a dense row, so a dot product costs R vector loads and 4R
-// FMAs per lane, and G dot products are reduced together with the butterfly
+// FMAs per lane, and U dot products are reduced together with the butterfly
 // above.  The list is sorted by row, so the A row stays in registers until
 // the row changes.  Results leave as one coalesced store per G nonzeros.
 // ---------------------------------------------------------------------------
@@ -98,13 +125,18 @@ __device__ __forceinline__ void sddmm_warp_unit(long long unit, long long nnz, c
     for (int base = 0; base < SDDMM_PER_SLOT; base += G) {
         const long long i = begin + base + gl;
         const bool ok = i < nnz;
-        const int my_r = ok ? __ldg(rowidx + i) : -1;
+        const int my_r = ok ? arows.ref(__ldg(rowidx + i)) : -1;
         const int my_c = ok ? __ldg(colidx + i) : -1;
-        T acc[G];
+        T my_out = 0;
+#if SP3_SDDMM_UNROLL_BATCH
 #pragma unroll
+#else
+#pragma unroll 1
+#endif
         for (int j = 0; j < G; j += UU) {
             int rr[UU], cc[UU];
             V b[UU][R];
+            T acc[UU];
 #pragma unroll
             for (int u = 0; u < UU; ++u) {
                 rr[u] = __shfl_sync(gmask, my_r, j + u, G);
@@ -121,7 +153,7 @@ __device__ __forceinline__ void sddmm_warp_unit(long long unit, long long nnz, c
             for (int u = 0; u < UU; ++u) {
                 if (rr[u] >= 0 && rr[u] != cur_row) {
                     cur_row = rr[u];
-                    const V* ap = arows.row(cur_row);
+                    const V* ap = arows.resolve(cur_row);
 #pragma unroll
                     for (int r = 0; r < R; ++r) {
                         const int v = gl + r * G;
@@ -131,11 +163,14 @@ __device__ __forceinline__ void sddmm_warp_unit(long long unit, long long nnz, c
                 T d = 0;
 #pragma unroll
                 for (int r = 0; r < R; ++r) d += vdot(a[r], b[u][r]);
-                acc[j + u] = d;
+                acc[u] = d;
             }
+            // UU dot products reduced together; value u ends up in lanes [u*G/UU, (u+1)*G/UU)
+            group_transpose_reduce<T, G, UU>(acc, gmask, gl);
+            const T mine = __shfl_sync(gmask, acc[0], (gl % UU) * (G / UU), G);
+            if (gl / UU == j / UU) my_out = mine;  // lane gl keeps nonzero gl of the batch
         }
-        group_transpose_reduce<T, G, G>(acc, gmask, gl);  // lane gl now holds nonzero gl of the batch
-        if (ok) store(i, acc[0]);
+        if (ok) store(i, my_out);
     }
 }
 
@@ -149,6 +184,7 @@ struct SpmmLong {
     void* carry;             // [total pieces, ldc] scratch
     long long ldc;           // elements per carry row
     int piece_len;           // nonzeros per piece
+    int* ticket;             // optional work counter (zero at launch): items are then handed out dynamically
 };
 
 template <typename T> struct EmitLocal {

@@ -201,7 +201,12 @@ class DistSpMM(_Dist3DOp):
         else:
             self.X_loc, self.Y_loc = self._alloc_local(p.col), self._alloc_local(p.row)
         self.X_owned = self.X_loc[:p.col.n_owned]
-        self.Y_owned = torch.zeros(p.row.n_owned, self.k_loc, dtype=dtype, device=self.device)
+        # sparse variants: the result is the owned head of the local Y block (no copy); fused and dense write
+        # into a buffer of their own
+        if variant in ("sparse", "sparseNRB"):
+            self.Y_owned = self.Y_loc[:p.row.n_owned]
+        else:
+            self.Y_owned = torch.zeros(p.row.n_owned, self.k_loc, dtype=dtype, device=self.device)
         self.sched = None
         if variant in ("sparse", "sparseNRB"):
             self.exX = self._exchange(p.col, self._col_group)
@@ -249,17 +254,16 @@ class DistSpMM(_Dist3DOp):
                     self._dense_row.reduce_scatter(self._Yslab, self.Y_owned)
                     self.Y_owned += prev
         else:
+            prev = self.Y_owned * beta if beta != 0.0 else None
             with t.span("comm1"):
                 self.exX.expand(self.X_loc)
             with t.span("comp"):
                 local.spmm(self.rowptr, self.rowidx, self.colidx, self.vals, self.X_loc, self.Y_loc, 0.0,
                            self.sched)
             with t.span("comm2"):
-                self.exY.reduce(self.Y_loc)
-                if beta == 0.0:
-                    self.Y_owned.copy_(self.Y_loc[:p.row.n_owned])
-                else:
-                    self.Y_owned.mul_(beta).add_(self.Y_loc[:p.row.n_owned])
+                self.exY.reduce(self.Y_loc)  # adds the peers' partial rows into the owned head = Y_owned
+                if prev is not None:
+                    self.Y_owned.add_(prev)
         self._finish()
         return self.Y_owned
 

@@ -103,6 +103,7 @@ class SpmmSchedule:
         self.first = torch.from_numpy(first).to(dev)
         self.npieces = torch.from_numpy(npieces).to(dev)
         self.counters = torch.zeros(max(1, first.shape[0]), dtype=torch.int32, device=dev)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
         self.total_pieces = int(npieces.sum())
         self.carry = None
         self.nlong = int(first.shape[0])
@@ -123,7 +124,7 @@ def spmm(rowptr, rowidx, colidx, vals, X, Y, beta, sched: SpmmSchedule | None):
     _ck(fn(rowptr.shape[0] - 1, sched.items.shape[0], native.ptr(sched.items), native.ptr(rowptr),
            native.ptr(colidx), native.ptr(vals), native.ptr(X), _ld(X), X.shape[1], float(beta), native.ptr(Y),
            _ld(Y), native.ptr(sched.first), native.ptr(sched.npieces), native.ptr(sched.counters),
-           native.ptr(carry), ldc, sched.piece_len, _stream()), "spmm")
+           native.ptr(carry), ldc, sched.piece_len, native.ptr(sched.ticket), _stream()), "spmm")
     return Y
 
 

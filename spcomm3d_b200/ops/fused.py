@@ -40,14 +40,14 @@ class _Comm(C.Structure):
 
 class _SddmmArgs(C.Structure):
     _fields_ = [("comm", _Comm), ("nnz", C.c_longlong), ("rowidx", P), ("colidx", P), ("sval", P),
-                ("a_rows", P), ("B_loc", P), ("ldb", C.c_longlong), ("n_owned_b", C.c_int),
+                ("a_refs", P), ("a_bases", P), ("world", C.c_int), ("B_loc", P), ("ldb", C.c_longlong), ("n_owned_b", C.c_int),
                 ("n_recv_b", C.c_int), ("b_src", P), ("nvec", C.c_int), ("Z", C.c_int), ("my_z", C.c_int),
                 ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P)]
 
 
 class _SpmmLong(C.Structure):
     _fields_ = [("first_piece", P), ("npieces", P), ("counters", P), ("carry", P), ("ldc", C.c_longlong),
-                ("piece_len", C.c_int)]
+                ("piece_len", C.c_int), ("ticket", P)]
 
 
 class _SpmmArgs(C.Structure):
@@ -201,9 +201,15 @@ class FusedSDDMM(_FusedBase):
         # A: only my owned rows live here (peers read them in place); the op's A_loc is that block
         self.A_loc = h.view("A", torch.float32, (p.row.n_owned, k))
         self.B_loc = h.view("B", torch.float32, (p.col.n_local, k))
-        a_own, a_need = self._side_tables(p.row, "A")
         _, b_need = self._side_tables(p.col, "B")
-        self.a_rows = self._dev_i64(np.concatenate([a_own, a_need]))
+        # A rows stay where they are: reference = owner rank << 25 | row inside the owner's block
+        if max(int(p.row.peer_owned.max(initial=0)), p.row.n_owned) >= 1 << 25:
+            raise ValueError("more than 2^25 owned rows on one rank")
+        row_ranks = np.asarray(_peer_ranks(p, "row"), dtype=np.int64)
+        refs = np.concatenate([(self.rank << 25) | np.arange(p.row.n_owned, dtype=np.int64),
+                               (row_ranks[p.row.recv_peer] << 25) | p.row.recv_src_idx.astype(np.int64)])
+        self.a_refs = self._dev_i32(refs if refs.size else [0])
+        self.a_bases = self._dev_i64([h.addr("A", r) for r in range(h.world)])
         self.b_src = self._dev_i64(b_need if b_need.size else [0])
         self.zwidth = p.nnz // Z + (1 if p.nnz % Z else 0)
         fiber = _peer_ranks(p, "fiber")
@@ -220,7 +226,7 @@ class FusedSDDMM(_FusedBase):
         self._fill_comm(a.comm, read_from, readers, others, others)
         a.nnz = p.nnz
         a.rowidx, a.colidx, a.sval = op.rowidx.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
-        a.a_rows = self.a_rows.data_ptr()
+        a.a_refs, a.a_bases, a.world = self.a_refs.data_ptr(), self.a_bases.data_ptr(), h.world
         a.B_loc, a.ldb = self.B_loc.data_ptr(), k
         a.n_owned_b, a.n_recv_b = p.col.n_owned, p.col.n_recv
         a.b_src = self.b_src.data_ptr()

@@ -7,8 +7,8 @@ _FILL = "p i64 i64 int i64 i64 int f64 u64 u64 p p"
 CUDA_SIGS = {
     "sp3_cuda_sddmm_f32": ("int", _SDDMM),
     "sp3_cuda_sddmm_f64": ("int", _SDDMM),
-    "sp3_cuda_spmm_f32": ("int", "int int p p p p p i64 int f32 p i64 p p p p i64 int p"),
-    "sp3_cuda_spmm_f64": ("int", "int int p p p p p i64 int f64 p i64 p p p p i64 int p"),
+    "sp3_cuda_spmm_f32": ("int", "int int p p p p p i64 int f32 p i64 p p p p i64 int p p"),
+    "sp3_cuda_spmm_f64": ("int", "int int p p p p p i64 int f64 p i64 p p p p i64 int p p"),
     "sp3_cuda_rows_f32": ("int", _ROWS),
     "sp3_cuda_rows_f64": ("int", _ROWS),
     "sp3_cuda_fill_rows_f32": ("int", _FILL),

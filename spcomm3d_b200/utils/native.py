@@ -131,6 +131,7 @@ def cuda_build_cmd(verbose_ptxas=False):
            "-Xcompiler", "-fvisibility=hidden", f"-I{CSRC / 'kernels'}"]
     if verbose_ptxas:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("SP3_NVCC_DEFS", "").split()  # e.g. "-DSP3_SDDMM_MINB=4" for tuning builds
     return cmd
 
 
