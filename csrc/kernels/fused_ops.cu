@@ -244,7 +244,7 @@ struct StoreSlices {
 };
 
 template <int G, int R, int U>
-__global__ void __launch_bounds__(256, SP3_SDDMM_MINB) fused_sddmm_kernel(const FusedSddmmArgs a) {
+__global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(const FusedSddmmArgs a) {
     const FusedComm& c = a.comm;
     const int lane = threadIdx.x & 31;
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);

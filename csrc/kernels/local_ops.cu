@@ -24,7 +24,7 @@ namespace sp3 {
 // warps stride over work units (see sddmm_warp_unit).
 // ---------------------------------------------------------------------------
 template <typename T, int G, int R, int U>
-__global__ void __launch_bounds__(256, SP3_SDDMM_MINB)
+__global__ void __launch_bounds__(256, sddmm_min_blocks(R))
 sddmm_vec_kernel(long long nnz, const int* __restrict__ rowidx, const int* __restrict__ colidx,
                  const T* __restrict__ sval, const T* __restrict__ A, long long lda,
                  const T* __restrict__ B, long long ldb, int nvec, T* __restrict__ out) {

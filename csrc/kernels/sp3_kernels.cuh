@@ -23,6 +23,8 @@ constexpr int SDDMM_PER_SLOT = 32;  // nonzeros per lane group; multiple of ever
 #ifndef SP3_SDDMM_MINB
 #define SP3_SDDMM_MINB 4
 #endif
+// With more than two vectors per lane the row registers alone need the larger budget of two blocks per SM.
+constexpr int sddmm_min_blocks(int R) { return R <= 2 ? SP3_SDDMM_MINB : 2; }
 #ifndef SP3_SDDMM_UNROLL_BATCH
 #define SP3_SDDMM_UNROLL_BATCH 1
 #endif
@@ -404,7 +406,9 @@ unsigned persistent_blocks(K kernel, long long needed, int threads = 256, size_t
 // with as many lanes per row as the row has vectors (measured on B200, R-MAT
 // scale 20, k = 32..256).  SP3_VEC_PER_LANE overrides R for tuning.
 inline void pick_shape(int nvec, int* G, int* R, bool spmm) {
-    static const int forced = env_int("SP3_VEC_PER_LANE", 0);
+    static const int forced_sddmm = env_int("SP3_VEC_PER_LANE", 0);
+    static const int forced_spmm = env_int("SP3_SPMM_VEC_PER_LANE", 0);
+    const int forced = spmm ? forced_spmm : forced_sddmm;
     int r = 1;
     if (!spmm) { r = 2; while (nvec > 16 * r && r < 8) r <<= 1; }
     if (forced > 0) r = forced;
