@@ -84,8 +84,11 @@ __device__ __forceinline__ int warp_ticket(int* ctr, int lane, int n = 1) {
     return __shfl_sync(0xffffffffu, t, 0);
 }
 
-constexpr int SDDMM_UNITS_PER_TICKET = 8;
-constexpr int SPMM_ITEMS_PER_TICKET = 4;
+// Work per ticket: large enough to keep the counter quiet, small enough that the last tickets (the tail of
+// the kernel, when other warps already idle) are short: about 1/32 of a warp's share, at most MAX.
+constexpr int SDDMM_UNITS_PER_TICKET_MAX = 8;
+constexpr int SPMM_ITEMS_PER_TICKET_MAX = 4;
+
 
 __device__ __forceinline__ bool aborted(const FusedComm& c) {
     return *reinterpret_cast<volatile int*>(c.ctrl + C_ABORT) != 0;
@@ -175,7 +178,14 @@ __device__ __forceinline__ void pull_rows(int r0, int r1, const float4* const* _
 // Every warp calls this after its MAIN work; the last one to arrive publishes
 // DONE and PART for this rank.
 __device__ __forceinline__ void main_epilogue(const FusedComm& c, int lane, int nwarps) {
-    __threadfence_system();
+    // remote stores (pushed partial results) must be visible system-wide before PART is signalled; a rank
+    // that pushed nothing only has to order its local writes
+#ifndef SP3_EPILOGUE_GPU_FENCE
+    if (c.n_push > 0) __threadfence_system();
+    else __threadfence();
+#else
+    __threadfence();
+#endif
     __syncwarp();
     int old = 0;
     if (lane == 0) old = atomicAdd(c.ctrl + C_MAIN_DONE, 1);
@@ -223,10 +233,18 @@ struct FusedSddmmArgs {
     long long zwidth;             // elements reserved per (parity, source) in a value buffer
     float* const* zbuf;           // [Z] value buffers of the fiber ranks (mine is local)
     float* out;                   // my slice of C
+    // Overlap of pulls and compute: the kernel walks the nonzeros in the order "those whose B row is owned
+    // first, then those that need a pulled row" (rowidx / colidx / sval are given in that order);
+    // orig[i] is the position of nonzero i in the plan's value order (null: identity), nnz_free the
+    // length of the first part, work_per_pull how many compute tickets a warp takes per pull ticket.
+    const int* orig;
+    long long nnz_free;
+    int work_per_pull;
 };
 
 struct StoreSlices {
     const float* sval;
+    const int* orig;
     float* out;
     float* const* zbuf;
     int Z, my_z, parity;
@@ -234,8 +252,9 @@ struct StoreSlices {
     long long zwidth;
     __device__ __forceinline__ void operator()(long long i, float dot) const {
         const float v = dot * __ldg(sval + i);
-        if (Z == 1) { out[i] = v; return; }
-        const unsigned ii = (unsigned)i, split = zrem * (zbase + 1);
+        const unsigned ii = orig ? (unsigned)__ldg(orig + i) : (unsigned)i;
+        if (Z == 1) { out[ii] = v; return; }
+        const unsigned split = zrem * (zbase + 1);
         unsigned zo, off;
         if (ii < split) { zo = ii / (zbase + 1); off = zo * (zbase + 1); }
         else { zo = zrem + (ii - split) / zbase; off = split + (zo - zrem) * zbase; }
@@ -254,39 +273,51 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
     __syncthreads();
     if (c.phases & PH_START) start_phase(c);
     if (c.phases & PH_MAIN) {
+        if (!(c.phases & PH_START) && blockIdx.x == 0 && threadIdx.x == 0) stamp(c, T_START);
         bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
         constexpr int SLOTS = 32 / G;
         const int n_pull = (a.n_recv_b + PULL_ROWS - 1) / PULL_ROWS;
         const long long per_unit = (long long)SLOTS * SDDMM_PER_SLOT;
         const long long n_units = (a.nnz + per_unit - 1) / per_unit;
         const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull};
-        const StoreSlices store{a.sval, a.out, a.zbuf, a.Z, a.my_z, parity, a.zbase, a.zrem, a.zwidth};
+        const StoreSlices store{a.sval, a.orig, a.out, a.zbuf, a.Z, a.my_z, parity, a.zbase, a.zrem, a.zwidth};
         float4* Bv = reinterpret_cast<float4*>(a.B_loc);
         const long long ldb_v = a.ldb / 4;
-        bool pulled = n_pull == 0;
-        // pull tickets first (one tile each), then compute tickets (several units each)
-        while (ok) {
+        bool pulled = n_pull == 0, pulls_left = n_pull > 0;
+        const long long n_free_units = a.nnz_free / per_unit;  // units that touch no pulled row
+        auto pull_one = [&]() -> bool {
             const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
-            if (t >= n_pull) break;
+            if (t >= n_pull) return false;
             const int r0 = t * PULL_ROWS;
             const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
             pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
             __threadfence();
             __syncwarp();
             if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
-        }
-        while (ok) {
-            const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
-            if (u0 >= n_units) break;
-            if (!pulled) {
-                ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
-                pulled = true;
-                if (!ok) break;
+            return true;
+        };
+        // A warp alternates one pull ticket with work_per_pull compute tickets, so remote rows stream in
+        // while units that need none of them are computed.  Before it waits for the pulls it helps to
+        // finish them; hence every pull ticket is taken by a running warp and the wait cannot deadlock.
+        bool more = true;
+        const int SDDMM_UNITS_PER_TICKET = per_ticket(n_units, nwarps, SDDMM_UNITS_PER_TICKET_MAX);
+        while (ok && more) {
+            if (pulls_left) pulls_left = pull_one();
+            for (int w = 0; w < a.work_per_pull && ok; ++w) {
+                const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
+                if (u0 >= n_units) { more = false; break; }
+                const long long u1 = u0 + SDDMM_UNITS_PER_TICKET < n_units ? u0 + SDDMM_UNITS_PER_TICKET : n_units;
+                if (!pulled && u1 > n_free_units) {
+                    while (pulls_left) pulls_left = pull_one();
+                    ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
+                    pulled = true;
+                    if (!ok) break;
+                }
+                for (long long u = u0; u < u1; ++u)
+                    sddmm_warp_unit<float, G, R, U>(u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
             }
-            const long long u1 = u0 + SDDMM_UNITS_PER_TICKET < n_units ? u0 + SDDMM_UNITS_PER_TICKET : n_units;
-            for (long long u = u0; u < u1; ++u)
-                sddmm_warp_unit<float, G, R, U>(u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
         }
+        while (ok && pulls_left) pulls_left = pull_one();  // no compute left but tiles remain (tiny blocks)
         main_epilogue(c, lane, nwarps);
     }
     if (c.phases & PH_FINISH) {
@@ -329,28 +360,34 @@ struct FusedSpmmArgs {
     int nvec;
     SpmmLong lg;
     int n_owned_y;
-    float* Ypart;                 // [n_owned_y, ldp] my own partial of the rows I own
-    long long ldp;
+    int n_crows;                  // owned rows that receive contributions from peers
+    const int* crows;             // [n_crows] their row numbers, ascending
     float4* const* y_dst;         // [rows I do not own] slot row address at the owner (parity 0)
     long long parity_off_v;       // float4 offset of the parity-1 slot buffer
     float* Y;                     // [n_owned_y, ldy] result
     long long ldy;
     float beta;
-    const long long* cptr;        // [n_owned_y + 1] contributions per owned row
+    const long long* cptr;        // [n_crows + 1] contributions per listed row
     const int* cslot;             // slot row of each contribution, ascending source rank
     const float* slots;           // my slot buffer (parity 0)
     long long lds;
 };
 
+// Rows I own go straight into the result (Y = beta*Y + my partial; the owners' FINISH phase then adds what
+// the peers pushed); rows I do not own are pushed into their slot at the owner.
 struct EmitOwnedOrPush {
-    float4* Ypart_v;
-    long long ldp_v;
+    float4* Yv;
+    long long ldy_v;
+    float beta;
     int n_owned;
     float4* const* y_dst;
     long long parity_off_v;
     __device__ __forceinline__ void operator()(int row, int v, const float4& acc) const {
-        if (row < n_owned) Ypart_v[(long long)row * ldp_v + v] = acc;
-        else __stcs(ldg_ptr(y_dst + (row - n_owned)) + parity_off_v + v, acc);
+        if (row < n_owned) {
+            float4* y = Yv + (long long)row * ldy_v + v;
+            if (beta != 0.f) { float4 o = vscale(beta, *y); vadd(o, acc); *y = o; }
+            else *y = acc;
+        } else __stcs(ldg_ptr(y_dst + (row - n_owned)) + parity_off_v + v, acc);
     }
 };
 
@@ -362,11 +399,12 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
     const int parity = c.epoch & 1;
     if (c.phases & PH_START) start_phase(c);
     if (c.phases & PH_MAIN) {
+        if (!(c.phases & PH_START) && blockIdx.x == 0 && threadIdx.x == 0) stamp(c, T_START);
         bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
         const int n_pull = (a.n_recv_x + PULL_ROWS - 1) / PULL_ROWS;
         float4* Xv = reinterpret_cast<float4*>(a.X_loc);
         const long long ldx_v = a.ldx / 4;
-        const EmitOwnedOrPush emit{reinterpret_cast<float4*>(a.Ypart), a.ldp / 4, a.n_owned_y, a.y_dst,
+        const EmitOwnedOrPush emit{reinterpret_cast<float4*>(a.Y), a.ldy / 4, a.beta, a.n_owned_y, a.y_dst,
                                    parity ? a.parity_off_v : 0};
         bool pulled = n_pull == 0;
         while (ok) {
@@ -379,6 +417,7 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
             __syncwarp();
             if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
         }
+        const int SPMM_ITEMS_PER_TICKET = per_ticket(a.nitems, nwarps, SPMM_ITEMS_PER_TICKET_MAX);
         while (ok) {
             const int i0 = warp_ticket(c.ctrl + C_TICKET_WORK, lane, SPMM_ITEMS_PER_TICKET);
             if (i0 >= a.nitems) break;
@@ -398,25 +437,26 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
         bool ok = wait_all(c, F_PART, c.contrib, c.n_contrib, W_PART);
         // my own partial rows come from my own MAIN warps (same launch): wait for all of them
         if (ok && (c.phases & PH_MAIN)) ok = wait_counter(c, C_MAIN_DONE, nwarps, W_PART);
-        const int n_chunks = (a.n_owned_y + REDUCE_ROWS - 1) / REDUCE_ROWS;
-        const float4* Pv = reinterpret_cast<const float4*>(a.Ypart);
+        // only rows that receive contributions are touched: crows lists them, cptr/cslot their slot rows in
+        // ascending source order
+        const int n_chunks = (a.n_crows + REDUCE_ROWS - 1) / REDUCE_ROWS;
         const float4* Sv = reinterpret_cast<const float4*>(a.slots) + (parity ? a.parity_off_v : 0);
         float4* Yv = reinterpret_cast<float4*>(a.Y);
-        const long long ldp_v = a.ldp / 4, lds_v = a.lds / 4, ldy_v = a.ldy / 4;
+        const long long lds_v = a.lds / 4, ldy_v = a.ldy / 4;
         while (ok) {
             const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
             if (t >= n_chunks) break;
             const int r0 = t * REDUCE_ROWS;
-            const int r1 = r0 + REDUCE_ROWS < a.n_owned_y ? r0 + REDUCE_ROWS : a.n_owned_y;
+            const int r1 = r0 + REDUCE_ROWS < a.n_crows ? r0 + REDUCE_ROWS : a.n_crows;
             const int total = (r1 - r0) * a.nvec;
             for (int e = lane; e < total; e += 32) {
-                const int row = r0 + e / a.nvec, v = e % a.nvec;
-                float4 s = __ldcg(Pv + (long long)row * ldp_v + v);
-                for (long long p = a.cptr[row]; p < a.cptr[row + 1]; ++p)
-                    vadd(s, __ldcg(Sv + (long long)a.cslot[p] * lds_v + v));
+                const int ci = r0 + e / a.nvec, v = e % a.nvec;
+                const int row = __ldg(a.crows + ci);
                 float4* y = Yv + (long long)row * ldy_v + v;
-                if (a.beta != 0.f) { float4 o = vscale(a.beta, *y); vadd(o, s); *y = o; }
-                else *y = s;
+                float4 s = *y;
+                for (long long p = a.cptr[ci]; p < a.cptr[ci + 1]; ++p)
+                    vadd(s, __ldcg(Sv + (long long)a.cslot[p] * lds_v + v));
+                *y = s;
             }
         }
         finish_epilogue(c, lane, nwarps);

@@ -83,12 +83,13 @@ spmm_items_kernel(int nitems, const int4* __restrict__ items, const long long* _
     if (lg.ticket) {
         // dynamic hand-out, SPMM_ITEMS_PER_STEP items per ticket: rows of a power-law matrix differ too much in
         // cost for a fixed assignment to balance
+        const int step = per_ticket(nitems, nwarps, SPMM_ITEMS_PER_STEP);
         for (;;) {
             int base = 0;
-            if (lane == 0) base = atomicAdd(lg.ticket, SPMM_ITEMS_PER_STEP);
+            if (lane == 0) base = atomicAdd(lg.ticket, step);
             base = __shfl_sync(0xffffffffu, base, 0);
             if (base >= nitems) break;
-            for (int it = base; it < base + SPMM_ITEMS_PER_STEP && it < nitems; ++it)
+            for (int it = base; it < base + step && it < nitems; ++it)
                 spmm_warp_item<T, G, R, U>(__ldg(items + it), rowptr, colidx, val, reinterpret_cast<const V*>(X),
                                            ldx / Vec<T>::N, nvec, emit, lg, lane);
         }

@@ -382,6 +382,12 @@ __device__ __forceinline__ void spmm_warp_item(const int4 item, const long long*
     if (lane == 0) lg.counters[lr] = 0;
 }
 
+// Work items per ticket of a dynamically scheduled kernel: about 1/32 of a warp's share, at most max_per.
+__device__ __forceinline__ int per_ticket(long long n_work, int nwarps, int max_per) {
+    const long long p = n_work / ((long long)nwarps * 32);
+    return p < 1 ? 1 : (p > max_per ? max_per : (int)p);
+}
+
 // ---- launch helpers ----------------------------------------------------------
 inline int env_int(const char* name, int dflt) {
     const char* e = getenv(name);

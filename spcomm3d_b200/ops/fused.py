@@ -42,7 +42,8 @@ class _SddmmArgs(C.Structure):
     _fields_ = [("comm", _Comm), ("nnz", C.c_longlong), ("rowidx", P), ("colidx", P), ("sval", P),
                 ("a_refs", P), ("a_bases", P), ("world", C.c_int), ("B_loc", P), ("ldb", C.c_longlong), ("n_owned_b", C.c_int),
                 ("n_recv_b", C.c_int), ("b_src", P), ("nvec", C.c_int), ("Z", C.c_int), ("my_z", C.c_int),
-                ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P)]
+                ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P),
+                ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int)]
 
 
 class _SpmmLong(C.Structure):
@@ -53,8 +54,8 @@ class _SpmmLong(C.Structure):
 class _SpmmArgs(C.Structure):
     _fields_ = [("comm", _Comm), ("nitems", C.c_int), ("items", P), ("rowptr", P), ("colidx", P), ("val", P),
                 ("X_loc", P), ("ldx", C.c_longlong), ("n_owned_x", C.c_int), ("n_recv_x", C.c_int),
-                ("x_src", P), ("nvec", C.c_int), ("lg", _SpmmLong), ("n_owned_y", C.c_int), ("Ypart", P),
-                ("ldp", C.c_longlong), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
+                ("x_src", P), ("nvec", C.c_int), ("lg", _SpmmLong), ("n_owned_y", C.c_int), ("n_crows", C.c_int),
+                ("crows", P), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
                 ("ldy", C.c_longlong), ("beta", C.c_float), ("cptr", P), ("cslot", P), ("slots", P),
                 ("lds", C.c_longlong)]
 
@@ -194,7 +195,8 @@ class FusedSDDMM(_FusedBase):
         return {"pad": F_KINDS * MAX_RANKS * 4, "A": plan.row.n_owned * rb, "B": plan.col.n_local * rb,
                 "zbuf": 2 * Z * zwidth * 4 if Z > 1 else 0}
 
-    def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0):
+    def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
+                 overlap: bool = True):
         super().__init__(op, heap, fabric, timeout_s)
         p, h, k = self.plan, self.heap, self.k_loc
         Z, z = p.mesh.Z, p.coords[2]
@@ -225,7 +227,23 @@ class FusedSDDMM(_FusedBase):
         others = [r for r in fiber if r != self.rank] if Z > 1 else []
         self._fill_comm(a.comm, read_from, readers, others, others)
         a.nnz = p.nnz
-        a.rowidx, a.colidx, a.sval = op.rowidx.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
+        # nonzeros whose B row is owned first (computable while the pulls are in flight), the others after
+        # them; both parts keep the row-sorted order, results are stored at their position in the plan's order
+        if overlap and p.col.n_recv > 0 and p.nnz > 0:
+            needs_pull = p.colidx >= p.col.n_owned
+            order = np.argsort(needs_pull, kind="stable")
+            nnz_free = int(p.nnz - needs_pull.sum())
+            self._perm = (self._dev_i32(p.rowidx[order]), self._dev_i32(p.colidx[order]),
+                          torch.from_numpy(p.vals[order]).to(device=self.device, dtype=torch.float32),
+                          self._dev_i32(order))
+            a.rowidx, a.colidx, a.sval, a.orig = (t.data_ptr() for t in self._perm)
+            a.nnz_free = nnz_free
+            nnz_per_ticket = 4 * 64  # a few units of 32..64 nonzeros (the kernel sizes tickets itself)
+            n_pull = -(-p.col.n_recv // 64)
+            a.work_per_pull = max(1, min(64, (nnz_free // nnz_per_ticket) // max(1, n_pull)))
+        else:
+            a.rowidx, a.colidx, a.sval = op.rowidx.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
+            a.orig, a.nnz_free, a.work_per_pull = None, 0, 1 << 30
         a.a_refs, a.a_bases, a.world = self.a_refs.data_ptr(), self.a_bases.data_ptr(), h.world
         a.B_loc, a.ldb = self.B_loc.data_ptr(), k
         a.n_owned_b, a.n_recv_b = p.col.n_owned, p.col.n_recv
@@ -259,8 +277,8 @@ class FusedSpMM(_FusedBase):
         p, h, k, rb = self.plan, self.heap, self.k_loc, self.row_bytes
         rp = p.row
         self.X_loc = h.view("X", torch.float32, (p.col.n_local, k))
-        # the op's Y_loc is only used for its owned rows here: my own partial of the rows I own
-        self.Y_loc = torch.zeros(max(rp.n_owned, 1), k, dtype=torch.float32, device=self.device)
+        # no local Y block: owned rows are written straight into the result, the others into their owners' slots
+        self.Y_loc = None
         _, x_need = self._side_tables(p.col, "X")
         self.x_src = self._dev_i64(x_need if x_need.size else [0])
         half = h.sizes["slots"] // 2
@@ -275,9 +293,12 @@ class FusedSpMM(_FusedBase):
         self.y_dst = self._dev_i64(y_dst if y_dst.size else [0])
         # contributions to my owned rows: slot rows grouped by owned row, ascending source
         order = np.argsort(rp.send_idx, kind="stable")
-        cptr = np.zeros(rp.n_owned + 1, np.int64)
-        np.cumsum(np.bincount(rp.send_idx, minlength=rp.n_owned), out=cptr[1:])
+        counts = np.bincount(rp.send_idx, minlength=rp.n_owned)
+        crows = np.flatnonzero(counts)
+        cptr = np.zeros(crows.size + 1, np.int64)
+        np.cumsum(counts[crows], out=cptr[1:])
         self.cptr = self._dev_i64(cptr)
+        self.crows = self._dev_i32(crows if crows.size else [0])
         self.cslot = self._dev_i32(order if order.size else [0])
         self.sched = cuda_ops.SpmmSchedule(op.rowptr)
         carry, ldc = self.sched.carry_for(k, torch.float32, self.device)
@@ -300,7 +321,7 @@ class FusedSpMM(_FusedBase):
         a.lg.ldc = ldc if carry is not None else k
         a.lg.piece_len = self.sched.piece_len
         a.n_owned_y = rp.n_owned
-        a.Ypart, a.ldp = self.Y_loc.data_ptr(), k
+        a.n_crows, a.crows = int(crows.size), self.crows.data_ptr()
         a.y_dst = self.y_dst.data_ptr()
         a.parity_off_v = half // 16
         a.cptr, a.cslot = self.cptr.data_ptr(), self.cslot.data_ptr()

@@ -25,9 +25,10 @@ def _setup(meshstr, gen, k, seed=3):
 MESHES = ["2x2x2", "4x2x1", "1x1x8", "2x1x2", "1x2x1", "3x2x1"]
 
 
+@pytest.mark.parametrize("overlap", [True, False])
 @pytest.mark.parametrize("meshstr", MESHES)
 @pytest.mark.parametrize("gen,k", [("uniform:600:500:7", 64), ("zipf:700:900:1.6:600", 32)])
-def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k):
+def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap):
     from spcomm3d_b200.models.dist_ops import DistSDDMM
     from spcomm3d_b200.ops import oracle
     from spcomm3d_b200.ops.fused import FusedSDDMM, run_lockstep
@@ -38,7 +39,8 @@ def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k):
     fabric = LocalFabric(mesh.size)
     kl = [split_k(k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
     heaps = fabric.heaps([FusedSDDMM.region_sizes(plans[r], kl[r]) for r in range(mesh.size)])
-    ops = [DistSDDMM(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0)
+    ops = [DistSDDMM(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0,
+                     overlap=overlap)
            for r in range(mesh.size)]
     for epoch in range(2):
         for op in ops:
