@@ -11,9 +11,10 @@
 //   * reads the row-side operand of SDDMM (A rows) directly from the owner's
 //     memory -- each such row is consumed by one work unit, so it crosses
 //     NVLink exactly once and is never staged;
-//   * SDDMM: stores every partial dot product directly into the value buffer
-//     of the fiber rank that owns that nonzero after the Z reduction, and then
-//     sums the Z partial vectors of its own slice (the reduce-scatter of
+//   * SDDMM: keeps its partial dot products in a local array and, as soon as
+//     all of them exist, stores the slice of every other fiber rank into that
+//     rank's value buffer with contiguous, coalesced remote stores; each rank
+//     then sums the Z partial vectors of its own slice (the reduce-scatter of
 //     src/denseComm.hpp:35-40 becomes remote stores + a local sum);
 //   * SpMM: stores finished partial rows of rows it does not own directly into
 //     a slot in the owner's memory; the owner adds its own partial and the
@@ -45,12 +46,13 @@ namespace sp3 {
 
 constexpr int MAX_RANKS = 64;
 enum FlagKind : int { F_READY = 0, F_DONE = 1, F_PART = 2, F_KINDS = 3 };
-enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_TICKET_WORK = 6, C_WORDS = 8 };
+enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_TICKET_WORK = 6, C_WORK_DONE = 7, C_TICKET_PUSH = 8, C_WORDS = 16 };
 enum Phase : int { PH_START = 1, PH_MAIN = 2, PH_FINISH = 4 };
-enum WaitSite : int { W_READY = 1, W_PULLS = 2, W_PART = 3, W_DONE = 4 };
+enum WaitSite : int { W_READY = 1, W_PULLS = 2, W_PART = 3, W_DONE = 4, W_WORK = 5 };
 
 constexpr int PULL_ROWS = 64;      // dense rows per pull ticket
 constexpr int REDUCE_ELEMS = 2048; // values per SDDMM reduce ticket
+constexpr int PUSH_ELEMS = 4096;   // partial values per SDDMM push ticket
 constexpr int REDUCE_ROWS = 32;    // owned rows per SpMM reduce ticket
 
 struct FusedComm {
@@ -233,6 +235,9 @@ struct FusedSddmmArgs {
     long long zwidth;             // elements reserved per (parity, source) in a value buffer
     float* const* zbuf;           // [Z] value buffers of the fiber ranks (mine is local)
     float* out;                   // my slice of C
+    float* part;                  // [nnz] local partial values (used when Z > 1)
+    int direct_push;              // 1: values of other fiber ranks are stored remotely as they are computed;
+                                  // 0: they are staged in `part` and pushed in bulk (narrow rows)
     // Overlap of pulls and compute: the kernel walks the nonzeros in the order "those whose B row is owned
     // first, then those that need a pulled row" (rowidx / colidx / sval are given in that order);
     // orig[i] is the position of nonzero i in the plan's value order (null: identity), nnz_free the
@@ -242,25 +247,35 @@ struct FusedSddmmArgs {
     int work_per_pull;
 };
 
-struct StoreSlices {
+// Where a value goes.  Z == 1: into the result.  Z > 1, staged mode: into the local array `part` at its
+// position in the plan's value order; the slices of the other fiber ranks are then pushed in bulk by the
+// push tickets of the MAIN phase.  Z > 1, direct mode: values of my own slice into `part`, the others
+// straight into their owner's buffer.
+struct StorePartial {
     const float* sval;
     const int* orig;
-    float* out;
-    float* const* zbuf;
-    int Z, my_z, parity;
+    float* dst;           // local: `part` (Z > 1, staged), or the result (Z == 1)
+    float* const* zbuf;   // direct mode: value buffers of the fiber ranks
+    int direct, Z, my_z, parity;
     unsigned zbase, zrem;
     long long zwidth;
     __device__ __forceinline__ void operator()(long long i, float dot) const {
-        const float v = dot * __ldg(sval + i);
         const unsigned ii = orig ? (unsigned)__ldg(orig + i) : (unsigned)i;
-        if (Z == 1) { out[ii] = v; return; }
+        const float v = dot * __ldg(sval + i);
+        if (!direct) { dst[ii] = v; return; }
+        // direct mode (wide rows: a lane group stores >= 32 contiguous bytes): straight into the owner's buffer
         const unsigned split = zrem * (zbase + 1);
         unsigned zo, off;
         if (ii < split) { zo = ii / (zbase + 1); off = zo * (zbase + 1); }
         else { zo = zrem + (ii - split) / zbase; off = split + (zo - zrem) * zbase; }
-        zbuf[zo][((long long)parity * Z + my_z) * zwidth + (ii - off)] = v;
+        if ((int)zo == my_z) dst[ii] = v;
+        else zbuf[zo][((long long)parity * Z + my_z) * zwidth + (ii - off)] = v;
     }
 };
+
+__device__ __forceinline__ long long slice_off(int z, unsigned zbase, unsigned zrem) {
+    return (long long)z * zbase + ((unsigned)z < zrem ? z : (int)zrem);
+}
 
 template <int G, int R, int U>
 __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(const FusedSddmmArgs a) {
@@ -280,7 +295,9 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         const long long per_unit = (long long)SLOTS * SDDMM_PER_SLOT;
         const long long n_units = (a.nnz + per_unit - 1) / per_unit;
         const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull};
-        const StoreSlices store{a.sval, a.orig, a.out, a.zbuf, a.Z, a.my_z, parity, a.zbase, a.zrem, a.zwidth};
+        const int direct = a.Z > 1 && a.direct_push;
+        const StorePartial store{a.sval, a.orig, a.Z > 1 ? a.part : a.out, a.zbuf, direct, a.Z, a.my_z, parity,
+                                 a.zbase, a.zrem, a.zwidth};
         float4* Bv = reinterpret_cast<float4*>(a.B_loc);
         const long long ldb_v = a.ldb / 4;
         bool pulled = n_pull == 0, pulls_left = n_pull > 0;
@@ -318,6 +335,33 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
             }
         }
         while (ok && pulls_left) pulls_left = pull_one();  // no compute left but tiles remain (tiny blocks)
+        if (a.Z > 1 && !direct) {
+            // all partial values of this rank are in `part` once every warp has passed this point; then the
+            // slices of the other fiber ranks travel as contiguous, fully coalesced remote stores
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(c.ctrl + C_WORK_DONE, 1);
+            if (ok) ok = wait_counter(c, C_WORK_DONE, nwarps, W_WORK);
+            const int cps = (int)((a.zwidth + PUSH_ELEMS - 1) / PUSH_ELEMS);
+            while (ok) {
+                const int t = warp_ticket(c.ctrl + C_TICKET_PUSH, lane);
+                if (t >= cps * a.Z) break;
+                const int z = t / cps, chunk = t % cps;
+                if (z == a.my_z) continue;
+                const long long len = a.zbase + ((unsigned)z < a.zrem ? 1 : 0);
+                const long long j0 = (long long)chunk * PUSH_ELEMS;
+                const long long j1 = j0 + PUSH_ELEMS < len ? j0 + PUSH_ELEMS : len;
+                const float* src = a.part + slice_off(z, a.zbase, a.zrem);
+                float* dst = a.zbuf[z] + ((long long)parity * a.Z + a.my_z) * a.zwidth;
+                for (long long j = j0 + lane; j < j1; j += 128) {
+                    float v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[u] = (j + 32 * u < j1) ? __ldcg(src + j + 32 * u) : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) if (j + 32 * u < j1) __stcs(dst + j + 32 * u, v[u]);
+                }
+            }
+        }
         main_epilogue(c, lane, nwarps);
     }
     if (c.phases & PH_FINISH) {
@@ -328,13 +372,15 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
             const long long my_len = a.zbase + ((unsigned)a.my_z < a.zrem ? 1 : 0);
             const int n_chunks = (int)((my_len + REDUCE_ELEMS - 1) / REDUCE_ELEMS);
             const float* mine = a.zbuf[a.my_z] + (long long)parity * a.Z * a.zwidth;
+            const float* own = a.part + slice_off(a.my_z, a.zbase, a.zrem);
             while (ok) {
                 const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
                 if (t >= n_chunks) break;
                 const long long e0 = (long long)t * REDUCE_ELEMS;
                 for (long long j = e0 + lane; j < e0 + REDUCE_ELEMS && j < my_len; j += 32) {
-                    float s = 0.f;
-                    for (int z = 0; z < a.Z; ++z) s += __ldcg(mine + (long long)z * a.zwidth + j);
+                    float s = 0.f;  // fiber ranks in ascending order; my own partial comes from `part`
+                    for (int z = 0; z < a.Z; ++z)
+                        s += z == a.my_z ? __ldcg(own + j) : __ldcg(mine + (long long)z * a.zwidth + j);
                     a.out[j] = s;
                 }
             }

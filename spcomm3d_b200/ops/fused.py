@@ -43,7 +43,7 @@ class _SddmmArgs(C.Structure):
                 ("a_refs", P), ("a_bases", P), ("world", C.c_int), ("B_loc", P), ("ldb", C.c_longlong), ("n_owned_b", C.c_int),
                 ("n_recv_b", C.c_int), ("b_src", P), ("nvec", C.c_int), ("Z", C.c_int), ("my_z", C.c_int),
                 ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P),
-                ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int)]
+                ("part", P), ("direct_push", C.c_int), ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int)]
 
 
 class _SpmmLong(C.Structure):
@@ -114,7 +114,7 @@ class _FusedBase:
         self.epoch = 0
         self.timeout_ns = int(timeout_s * 1e9)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.ctrl = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.ctrl = torch.zeros(16, dtype=torch.int32, device=self.device)
         self.pad = heap.view("pad", torch.int32, (F_KINDS * MAX_RANKS,))
         self.peer_pad = self._dev_i64([heap.addr("pad", r) for r in range(heap.world)])
         self._keep = []
@@ -196,7 +196,7 @@ class FusedSDDMM(_FusedBase):
                 "zbuf": 2 * Z * zwidth * 4 if Z > 1 else 0}
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
-                 overlap: bool = True):
+                 overlap: bool = True, direct_push: bool | None = None):
         super().__init__(op, heap, fabric, timeout_s)
         p, h, k = self.plan, self.heap, self.k_loc
         Z, z = p.mesh.Z, p.coords[2]
@@ -254,6 +254,10 @@ class FusedSDDMM(_FusedBase):
         a.zwidth = self.zwidth
         a.zbuf = self.zbuf_ptrs.data_ptr()
         a.out = self.out.data_ptr()
+        self.part = torch.zeros(p.nnz if Z > 1 else 1, dtype=torch.float32, device=self.device)
+        a.part = self.part.data_ptr()
+        # a lane group stores (k_loc/8) consecutive values at a time: direct remote stores only pay for >= 32 bytes
+        a.direct_push = int(direct_push if direct_push is not None else k >= 64)
 
     def launch(self, phases=PH_ALL, new_epoch=True):
         if new_epoch:
