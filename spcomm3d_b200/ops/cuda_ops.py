@@ -42,7 +42,27 @@ def _ld(t):
     return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
 
 
+USE_TMA = os.environ.get("SP3_SDDMM_TMA", "0") == "1"
+
+
+def sddmm_tma(rowidx, colidx, svals, A, B, out, status=None):
+    """SDDMM whose B rows are staged in shared memory by TMA `tile::gather4`
+    copies (csrc/kernels/tma_ops.cu).  fp32, k a multiple of 4 in [8, 256]."""
+    if A.dtype != torch.float32:
+        raise TypeError("the TMA kernel is fp32")
+    st = new_status(A.device) if status is None else status
+    rc = native.cuda().sp3_cuda_sddmm_tma_f32(rowidx.shape[0], native.ptr(rowidx), native.ptr(colidx),
+                                              native.ptr(svals), native.ptr(A), _ld(A), native.ptr(B), _ld(B),
+                                              B.shape[0], A.shape[1], native.ptr(out), native.ptr(st), _stream())
+    if rc < 0:
+        raise ValueError({-1: "shape not supported by the TMA kernel", -2: "tensor map encoding failed"}[rc])
+    _ck(rc, "sddmm_tma")
+    return out
+
+
 def sddmm(rowidx, colidx, svals, A, B, out):
+    if USE_TMA and A.dtype == torch.float32 and A.shape[1] % 4 == 0 and 8 <= A.shape[1] <= 256:
+        return sddmm_tma(rowidx, colidx, svals, A, B, out)
     fn = getattr(native.cuda(), f"sp3_cuda_sddmm_{_F[A.dtype]}")
     _ck(fn(rowidx.shape[0], native.ptr(rowidx), native.ptr(colidx), native.ptr(svals), native.ptr(A), _ld(A),
            native.ptr(B), _ld(B), A.shape[1], native.ptr(out), _stream()), "sddmm")
