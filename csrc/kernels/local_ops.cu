@@ -27,14 +27,14 @@ template <typename T, int G, int R, int U>
 __global__ void __launch_bounds__(256, sddmm_min_blocks(R))
 sddmm_vec_kernel(long long nnz, const int* __restrict__ rowidx, const int* __restrict__ colidx,
                  const T* __restrict__ sval, const T* __restrict__ A, long long lda,
-                 const T* __restrict__ B, long long ldb, int nvec, T* __restrict__ out) {
+                 const T* __restrict__ B, long long ldb, int nvec, T* __restrict__ out, const int* __restrict__ orig) {
     using V = typename Vec<T>::type;
     constexpr int SLOTS = 32 / G;
     const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     const int lane = threadIdx.x & 31;
     const RowsByStride<T> arows{reinterpret_cast<const V*>(A), lda / Vec<T>::N};
-    const StoreLocal<T> store{out, sval};
+    const StoreLocal<T> store{out, sval, orig};
     for (long long unit = warp0; unit * SLOTS * (long long)SDDMM_PER_SLOT < nnz; unit += nwarps)
         sddmm_warp_unit<T, G, R, U>(unit, nnz, rowidx, colidx, arows, reinterpret_cast<const V*>(B),
                                     ldb / Vec<T>::N, nvec, store, lane);
@@ -243,12 +243,13 @@ __global__ void touch_masks_kernel(long long nnz, const int* __restrict__ rows, 
 // ---- dispatch ---------------------------------------------------------------
 template <typename T>
 int launch_sddmm(long long nnz, const int* ri, const int* ci, const T* sv, const T* A, long long lda, const T* B,
-                 long long ldb, int k, T* out, cudaStream_t st) {
+                 long long ldb, int k, T* out, cudaStream_t st, const int* orig = nullptr) {
     if (nnz == 0) return 0;
     constexpr int VN = Vec<T>::N;
     const bool vec_ok = k % VN == 0 && lda % VN == 0 && ldb % VN == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)B % 16 == 0;
     const int nvec = k / VN;
     if (!vec_ok || nvec > 256) {
+        if (orig) return -1;  // the scatter form exists for the vector kernel only
         long long warps = nnz < (1ll << 22) ? nnz : (1ll << 22);
         sddmm_scalar_kernel<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(nnz, ri, ci, sv, A, lda, B, ldb, k, out);
         return (int)cudaGetLastError();
@@ -261,7 +262,7 @@ int launch_sddmm(long long nnz, const int* ri, const int* ci, const T* sv, const
 #define SP3_SDDMM(GG, RR)                                                                                      \
     sddmm_vec_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>                                                             \
         <<<persistent_blocks(sddmm_vec_kernel<T, GG, RR, (RR >= 8 ? 2 : 4)>, needed), 256, 0, st>>>(           \
-            nnz, ri, ci, sv, A, lda, B, ldb, nvec, out)
+            nnz, ri, ci, sv, A, lda, B, ldb, nvec, out, orig)
     SP3_DISPATCH_GR(SP3_SDDMM)
 #undef SP3_SDDMM
     return (int)cudaGetLastError();
@@ -317,6 +318,13 @@ using namespace sp3;
 SP3_API int sp3_cuda_sddmm_f32(long long nnz, const int* ri, const int* ci, const float* sv, const float* A,
                                long long lda, const float* B, long long ldb, int k, float* out, void* stream) {
     return launch_sddmm<float>(nnz, ri, ci, sv, A, lda, B, ldb, k, out, (cudaStream_t)stream);
+}
+// out[orig[i]] = sval[i] * <A[ri[i]], B[ci[i]]>: SDDMM over a subset of the nonzeros, results scattered to their
+// positions in the full value array (used next to the dense-panel kernel).
+SP3_API int sp3_cuda_sddmm_orig_f32(long long nnz, const int* ri, const int* ci, const float* sv, const float* A,
+                                    long long lda, const float* B, long long ldb, int k, float* out, const int* orig,
+                                    void* stream) {
+    return launch_sddmm<float>(nnz, ri, ci, sv, A, lda, B, ldb, k, out, (cudaStream_t)stream, orig);
 }
 SP3_API int sp3_cuda_sddmm_f64(long long nnz, const int* ri, const int* ci, const double* sv, const double* A,
                                long long lda, const double* B, long long ldb, int k, double* out, void* stream) {

@@ -94,8 +94,11 @@ template <typename T> struct RowsByPeerRef {
 template <typename T> struct StoreLocal {
     T* out;
     const T* sval;
+    const int* orig;  // optional: result position of nonzero i (null: i)
     __device__ __forceinline__ void operator()(long long i, T dot) const {
-        out[i] = sval ? dot * __ldg(sval + i) : dot;
+        const T v = sval ? dot * __ldg(sval + i) : dot;
+        if (orig) out[__ldg(orig + i)] = v;
+        else out[i] = v;
     }
 };
 

@@ -180,3 +180,35 @@ def test_sddmm_tma_gather(k):
     torch.cuda.synchronize()
     assert st.tolist()[0] == 0, st.tolist()
     assert (out.cpu().double() - ref).abs().max() <= 2e-5 * ref.abs().max() * k ** 0.5
+
+
+@pytest.mark.parametrize("k", [32, 64, 128])
+def test_sddmm_dense_panels_on_tensor_cores(k):
+    """Hub block x hub columns goes through tcgen05 TF32 tiles, the rest through the gather kernel."""
+    from spcomm3d_b200.ops.panel import PanelSDDMM
+    rng = np.random.default_rng(5)
+    nrows, ncols = 1000, 900
+    # a dense corner (rows 0..255 x 100 hub columns, 30 % filled) plus a sparse background
+    hub_cols = rng.choice(ncols, 100, replace=False)
+    rr, cc = np.nonzero(rng.random((256, 100)) < 0.3)
+    rows = np.concatenate([rr, rng.integers(0, nrows, 6000)])
+    cols = np.concatenate([hub_cols[cc], rng.integers(0, ncols, 6000)])
+    keys = np.unique(rows.astype(np.int64) * ncols + cols)
+    rows, cols = (keys // ncols).astype(np.int32), (keys % ncols).astype(np.int32)
+    vals = rng.random(keys.size)
+    op = PanelSDDMM(rows, cols, vals, nrows, ncols)
+    assert op.npanels >= 2 and op.n_panel_nnz > 5000 and op.n_panel_nnz + op.n_rest == keys.size
+    A = torch.from_numpy(rng.standard_normal((nrows, k))).float()
+    B = torch.from_numpy(rng.standard_normal((ncols, k))).float()
+    out = torch.full((keys.size,), float("nan"), dtype=torch.float32, device="cuda")
+    op.run(A.cuda(), B.cuda(), out)
+    torch.cuda.synchronize()
+    assert op.status.tolist()[0] == 0, op.status.tolist()
+    ref = (A.double()[rows.astype(np.int64)] * B.double()[cols.astype(np.int64)]).sum(1) * torch.from_numpy(vals)
+    err = (out.cpu().double() - ref).abs()
+    assert not torch.isnan(out).any()
+    # TF32 operands: ~2^-11 relative per product, sqrt(k) growth
+    assert err.max() <= 4e-3 * k ** 0.5
+    # the remainder went through the fp32 kernel and is tight
+    rest = op.r_pos.cpu().long()
+    assert err[rest].max() <= 2e-5 * max(1.0, ref.abs().max()) * k ** 0.5
