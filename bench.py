@@ -42,6 +42,9 @@ def parse_args():
     ap.add_argument("--variant", default=None, choices=[None, "fused", "sparse", "sparseNRB", "dense"])
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--panels", action="store_true",
+                    help="SDDMM: dense 128x64 panels on the tcgen05 tensor cores (TF32), rest on the gather kernel")
+    ap.add_argument("--min-col-nnz", type=int, default=3)
     return ap.parse_args()
 
 
@@ -138,7 +141,11 @@ def run_ours(args):
     gnnz = m.nnz
     del m
     setup_s = time.time() - t0
-    step = SddmmSpmmStep(plan, groups, args.k, torch.float32, device, variant, seed=args.seed)
+    kw = {"panels": True, "min_col_nnz": args.min_col_nnz} if args.panels else {}
+    step = SddmmSpmmStep(plan, groups, args.k, torch.float32, device, variant, seed=args.seed, **kw)
+    if args.panels and step.sddmm._panels is not None and rank == 0:
+        pn = step.sddmm._panels
+        print(f"# panels: {pn.npanels} tiles hold {pn.n_panel_nnz} of {pn.nnz} nonzeros", file=sys.stderr)
     step.fill_device_operands()
 
     def barrier():
@@ -207,7 +214,7 @@ def run_ours(args):
                                 "spmm_expand": vol_t[2].item(), "spmm_reduce": vol_t[3].item()},
         "gpu_launches": launches, "clocks": clocks.summary(), "e2e": e2e,
         "config": {"model": f"{args.gen} k={args.k} fp32 SDDMM then SpMM", "matrix": args.gen, "nnz": gnnz,
-                   "k": args.k, "mesh": str(mesh), "variant": variant, "global_batch": None, "seq_len": None,
+                   "k": args.k, "mesh": str(mesh), "variant": variant, "sddmm_precision": "tf32 panels + fp32" if args.panels else "fp32", "global_batch": None, "seq_len": None,
                    "parallelism": f"mesh{mesh}", "l2": "operands larger than L2 at every N; no flush",
                    "setup_s": round(setup_s, 1)},
     }

@@ -15,10 +15,13 @@
 // path is opt-in and tested with a matching tolerance.
 //
 // Shared-memory operand layout (K-major, no swizzle): 16-byte chunk c (4
-// floats of k) of row r lives at byte (c * ROWS + r) * 16.  A core matrix
-// (8 rows x 16 B) is 128 contiguous bytes; the next 8 rows are SBO = 128 B
-// away, the next k chunk LBO = ROWS * 16 B away.  One MMA consumes 8 floats of
-// k (two chunks).
+// floats of k) of row r lives at byte (c * (ROWS + 1) + r) * 16.  A core
+// matrix (8 rows x 16 B) is 128 contiguous bytes; the next 8 rows are SBO =
+// 128 B away, the next k chunk LBO = (ROWS + 1) * 16 B away (the extra 16 B per
+// chunk keep the staging stores of a warp, which writes one row = 32 chunks at
+// a time, on distinct banks).  One MMA consumes 8 floats of k (two chunks).
+// The accumulator tile is staged for sampling in the space of the A operand,
+// which is dead once the MMAs have completed.
 #include "sp3_cuda.cuh"
 
 namespace sp3 {
@@ -26,6 +29,12 @@ namespace sp3 {
 constexpr int PANEL_M = 128;   // rows per panel (TMEM lanes)
 constexpr int PANEL_N = 64;    // columns per panel (TMEM columns)
 constexpr unsigned PANEL_WAIT_TRIES = 1u << 22;
+
+// bytes of the A operand space: [k/4 chunks][129] float4, at least the 128 x 65 fp32 accumulator staging tile
+__host__ __device__ inline size_t panel_a_bytes(int k) {
+    const size_t a = (size_t)(k / 4) * (PANEL_M + 1) * 16, d = (size_t)PANEL_M * (PANEL_N + 1) * 4;
+    return ((a > d ? a : d) + 127) / 128 * 128;
+}
 
 __device__ __forceinline__ unsigned p_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -52,12 +61,14 @@ sddmm_panel_kernel(int npanels, const int* __restrict__ panel_row0, const int* _
                    const float* __restrict__ B, long long ldb, int k, float* __restrict__ out, int* status) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int nchunk = k / 4;
-    float4* sA = reinterpret_cast<float4*>(smem);                               // [nchunk][128]
-    float4* sB = sA + (size_t)nchunk * PANEL_M;                                 // [nchunk][64]
-    float* sD = reinterpret_cast<float*>(sB + (size_t)nchunk * PANEL_N);        // [128][65]
-    unsigned long long* bar = reinterpret_cast<unsigned long long*>(sD + PANEL_M * (PANEL_N + 1));
+    constexpr int LDA_S = PANEL_M + 1, LDB_S = PANEL_N + 1;                     // chunk strides in float4
+    const size_t a_bytes = panel_a_bytes(k);
+    float4* sA = reinterpret_cast<float4*>(smem);                               // [nchunk][129]
+    float* sD = reinterpret_cast<float*>(smem);                                 // [128][65], reuses the A space
+    float4* sB = reinterpret_cast<float4*>(smem + a_bytes);                     // [nchunk][65]
+    unsigned long long* bar = reinterpret_cast<unsigned long long*>(smem + a_bytes + (size_t)nchunk * LDB_S * 16);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bar + 1);
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const unsigned bar_addr = p_smem_u32(bar);
 
     if (tid == 0) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_addr));
@@ -75,15 +86,30 @@ sddmm_panel_kernel(int npanels, const int* __restrict__ panel_row0, const int* _
 
     for (int p = blockIdx.x; p < npanels && ok; p += gridDim.x) {
         const int r0 = panel_row0[p];
-        // stage A rows r0..r0+127 (thread t owns row t) and the panel's B rows (threads 0..63)
-        {
-            const int row = r0 + tid;
-            const float4* src = reinterpret_cast<const float4*>(A + (long long)(row < nrows_a ? row : r0) * lda);
-            for (int c = 0; c < nchunk; ++c) sA[(size_t)c * PANEL_M + tid] = __ldg(src + c);
-            if (tid < PANEL_N) {
-                const float4* bsrc = reinterpret_cast<const float4*>(B + (long long)panel_cols[(size_t)p * PANEL_N + tid] * ldb);
-                for (int c = 0; c < nchunk; ++c) sB[(size_t)c * PANEL_N + tid] = __ldg(bsrc + c);
+        // stage the 128 A rows and the 64 panel B rows: a warp reads one row per step, lane = 16-byte chunk
+        // (coalesced), four rows in flight
+        for (int rr = warp * 32; rr < warp * 32 + 32; rr += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int row = r0 + rr + u;
+                const float4* src = reinterpret_cast<const float4*>(A + (long long)(row < nrows_a ? row : r0) * lda);
+                v[u] = lane < nchunk ? __ldg(src + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (lane < nchunk) sA[(size_t)lane * LDA_S + rr + u] = v[u];
+        }
+        for (int rr = warp * 16; rr < warp * 16 + 16; rr += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4* src = reinterpret_cast<const float4*>(B + (long long)panel_cols[(size_t)p * PANEL_N + rr + u] * ldb);
+                v[u] = lane < nchunk ? __ldg(src + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (lane < nchunk) sB[(size_t)lane * LDB_S + rr + u] = v[u];
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
         __syncthreads();
@@ -91,8 +117,8 @@ sddmm_panel_kernel(int npanels, const int* __restrict__ panel_row0, const int* _
             const unsigned a0 = p_smem_u32(sA), b0 = p_smem_u32(sB);
             const unsigned idesc = umma_idesc_tf32(PANEL_M, PANEL_N);
             for (int s = 0; s < k / 8; ++s) {  // 8 floats of k = two 16-byte chunks per MMA
-                const unsigned long long da = umma_desc(a0 + (unsigned)s * 2u * PANEL_M * 16u, PANEL_M * 16u, 128u);
-                const unsigned long long db = umma_desc(b0 + (unsigned)s * 2u * PANEL_N * 16u, PANEL_N * 16u, 128u);
+                const unsigned long long da = umma_desc(a0 + (unsigned)s * 2u * LDA_S * 16u, LDA_S * 16u, 128u);
+                const unsigned long long db = umma_desc(b0 + (unsigned)s * 2u * LDB_S * 16u, LDB_S * 16u, 128u);
                 const unsigned acc = s > 0;
                 asm volatile(
                     "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
@@ -157,13 +183,17 @@ SP3_API int sp3_cuda_sddmm_panel_f32(int npanels, const int* panel_row0, const i
                                      long long ldb, int k, float* out, int* status, void* stream) {
     if (npanels == 0) return 0;
     if (k % 8 || k < 8 || k > 128 || lda % 4 || ldb % 4 || (uintptr_t)A % 16 || (uintptr_t)B % 16) return -1;
-    const size_t smem = (size_t)(k / 4) * (PANEL_M + PANEL_N) * 16 + (size_t)PANEL_M * (PANEL_N + 1) * 4 + 16;
+    const size_t smem = panel_a_bytes(k) + (size_t)(k / 4) * (PANEL_N + 1) * 16 + 16;
     cudaError_t e = cudaFuncSetAttribute(sddmm_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(sddmm_panel_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int blocks = npanels < sms ? npanels : sms;
+    int per_sm = 1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sddmm_panel_kernel, 128, smem);
+    if (per_sm < 1) per_sm = 1;
+    const int blocks = npanels < sms * per_sm ? npanels : sms * per_sm;
     sddmm_panel_kernel<<<blocks, 128, smem, (cudaStream_t)stream>>>(npanels, panel_row0, panel_cols, panel_ptr, e_row, e_col,
                                                                     e_pos, e_sval, A, lda, nrows_a, B, ldb, k, out, status);
     return (int)cudaGetLastError();

@@ -138,6 +138,12 @@ class DistSDDMM(_Dist3DOp):
             self.exB = self._exchange(p.col, self._col_group)
         if variant != "fused":
             self.fiber = FiberReduce(p.nnz, self.mesh.Z, p.coords[2], self._fiber_group, dtype, self.device)
+        # opt-in: dense (128-row x 64-column) panels on the tensor cores (TF32), the rest on the gather kernel
+        self._panels = None
+        if kw.get("panels") and variant in ("sparse", "sparseNRB") and self.device.type == "cuda":
+            from ..ops.panel import PanelSDDMM
+            self._panels = PanelSDDMM(p.rowidx, p.colidx, p.vals, p.row.n_local, p.col.n_local, self.device,
+                                      **{k_: v for k_, v in kw.items() if k_ in ("min_col_nnz", "min_panel_nnz")})
         self.owned_off, self.owned_len = p.owned_nnz_slice()
 
     def _local_buffers(self):
@@ -162,7 +168,10 @@ class DistSDDMM(_Dist3DOp):
                 self.exA.expand(self.A_loc)
                 self.exB.expand(self.B_loc)
             with t.span("comp"):
-                local.sddmm(self.rowidx, self.colidx, self.vals, self.A_loc, self.B_loc, out=self.partial)
+                if self._panels is not None:
+                    self._panels.run(self.A_loc, self.B_loc, self.partial)
+                else:
+                    local.sddmm(self.rowidx, self.colidx, self.vals, self.A_loc, self.B_loc, out=self.partial)
             with t.span("comm2"):
                 c = self.fiber(self.partial)
         if self.mesh.Z == 1:

@@ -23,10 +23,11 @@ STREAM_A, STREAM_B = 1, 2
 
 
 class SddmmSpmmStep:
-    def __init__(self, plan, groups, k, dtype=torch.float32, device="cuda", variant="sparseNRB", seed=0):
+    def __init__(self, plan, groups, k, dtype=torch.float32, device="cuda", variant="sparseNRB", seed=0,
+                 **sddmm_kw):
         self.plan, self.k, self.seed = plan, k, seed
         self.device = torch.device(device)
-        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant)
+        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant, **sddmm_kw)
         self.spmm = DistSpMM(plan, groups, k, dtype, device, variant)
         self.host = None
 
