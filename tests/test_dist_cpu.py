@@ -80,3 +80,47 @@ def test_distributed_reader(tmp_path):
     path = str(tmp_path / "m.bin")
     binfmt.write_bin(path, m)
     run_ranks(_check_many, 8, "2x2x2", [("sddmm", "sparseNRB"), ("spmm", "sparse")], K, path)
+
+
+def _config1_rank(rank, world):
+    """BASELINE config 1: 4096 x 4096, 16 nonzeros per row, A and B 4096 x 32 fp64 N(0,1), 2x2x2, checked
+    element-wise against the serial result; then the attention-style chain on the same mesh."""
+    from spcomm3d_b200.models.dist_ops import DistSDDMM
+    from spcomm3d_b200.models.layer import GatLayer
+    from spcomm3d_b200.ops import oracle
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups, split_k
+    from spcomm3d_b200.parallel.plan import build_my_plan
+    from spcomm3d_b200.utils import generate
+    from spcomm3d_b200.utils.sparse import CooMatrix
+    mesh = Mesh3D(2, 2, 2)
+    groups = MeshGroups.create(mesh)
+    M = N = 4096
+    k = 32
+    m = generate.fixed_degree(M, N, 16, seed=1)
+    _, plan = build_my_plan(m, mesh, rank, seed=1)
+    A = generate.fill_rows(np.arange(M), k, 0, k, seed=2, stream=1, dtype=np.float64)
+    B = generate.fill_rows(np.arange(N), k, 0, k, seed=2, stream=2, dtype=np.float64)
+    op = DistSDDMM(plan, groups, k, torch.float64, "cpu", "sparseNRB")
+    op.fill_owned(op.A_owned, plan.row.owned_gids, seed=2, stream=1)
+    op.fill_owned(op.B_owned, plan.col.owned_gids, seed=2, stream=2)
+    op.poison_unowned()
+    c = op.run()
+    off, ln = plan.owned_nnz_slice()
+    mine = CooMatrix(M, N, plan.global_rows()[off:off + ln], plan.global_cols()[off:off + ln], plan.vals[off:off + ln])
+    torch.testing.assert_close(c, oracle.sddmm_ref(mine, A, B), rtol=1e-12, atol=1e-12)
+    # chain: Y = (S o (A B^T)) X with X = B
+    layer = GatLayer(plan, groups, k, torch.float64, "cpu", "sparseNRB")
+    for o_ in (layer.sddmm,):
+        o_.fill_owned(o_.A_owned, plan.row.owned_gids, seed=2, stream=1)
+        o_.fill_owned(o_.B_owned, plan.col.owned_gids, seed=2, stream=2)
+    layer.spmm.fill_owned(layer.spmm.X_owned, plan.col.owned_gids, seed=2, stream=2)
+    y = layer.run()
+    scores = oracle.sddmm_ref(m, A, B)
+    cm = CooMatrix(M, N, m.rows, m.cols, scores.numpy())
+    ko, kw = split_k(k, mesh.Z, groups.coords[2])
+    ref = oracle.spmm_ref(cm, B)[plan.row.owned_gids][:, ko:ko + kw]
+    torch.testing.assert_close(y, ref, rtol=1e-10, atol=1e-10)
+
+
+def test_baseline_config1_and_chain():
+    run_ranks(_config1_rank, 8)
