@@ -154,25 +154,26 @@ __device__ __forceinline__ void start_phase(const FusedComm& c) {
 
 // Copies dense rows [r0, r1) of a receive list from their owners' memory
 // (src[r] = absolute address of the row, local or peer) into the local block.
-// The tile is treated as a flat list of 16-byte vectors, four per lane in
-// flight, so a warp keeps 2 KB of NVLink reads outstanding.
+// The tile is treated as a flat list of 16-byte vectors, eight per lane in
+// flight, so a warp keeps 4 KB of NVLink reads outstanding.
 __device__ __forceinline__ void pull_rows(int r0, int r1, const float4* const* __restrict__ src,
                                           float4* __restrict__ dst, long long ld_v, int nvec, int lane) {
     const int total = (r1 - r0) * nvec;
-    for (int base = 0; base < total; base += 128) {
-        float4 v[4];
-        int row[4], vec[4];
+    constexpr int PU = 8;
+    for (int base = 0; base < total; base += 32 * PU) {
+        float4 v[PU];
+        int row[PU], vec[PU];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < PU; ++u) {
             const int e = base + u * 32 + lane;
             row[u] = e < total ? e / nvec : -1;
             vec[u] = e - row[u] * nvec;
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < PU; ++u)
             if (row[u] >= 0) v[u] = __ldcs(ldg_ptr(src + r0 + row[u]) + vec[u]);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < PU; ++u)
             if (row[u] >= 0) dst[(long long)(r0 + row[u]) * ld_v + vec[u]] = v[u];
     }
 }
@@ -245,6 +246,11 @@ struct FusedSddmmArgs {
     const int* orig;
     long long nnz_free;
     int work_per_pull;
+    // Staging of remote A rows (optional; n_recv_a == 0: A rows are read in place from their owners): the needed
+    // rows a_src[0..n_recv_a) are pulled to A_stage, which follows my owned rows in my own A block.
+    int n_recv_a;
+    const float4* const* a_src;
+    float* A_stage;
 };
 
 // Where a value goes.  Z == 1: into the result.  Z > 1, staged mode: into the local array `part` at its
@@ -291,7 +297,9 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         if (!(c.phases & PH_START) && blockIdx.x == 0 && threadIdx.x == 0) stamp(c, T_START);
         bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
         constexpr int SLOTS = 32 / G;
-        const int n_pull = (a.n_recv_b + PULL_ROWS - 1) / PULL_ROWS;
+        // pull tickets: tiles of needed A rows first (when A rows are staged), then tiles of needed B rows
+        const int n_pull_a = (a.n_recv_a + PULL_ROWS - 1) / PULL_ROWS;
+        const int n_pull = n_pull_a + (a.n_recv_b + PULL_ROWS - 1) / PULL_ROWS;
         const long long per_unit = (long long)SLOTS * SDDMM_PER_SLOT;
         const long long n_units = (a.nnz + per_unit - 1) / per_unit;
         const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull};
@@ -305,34 +313,41 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         auto pull_one = [&]() -> bool {
             const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
             if (t >= n_pull) return false;
-            const int r0 = t * PULL_ROWS;
-            const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
-            pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
+            if (t < n_pull_a) {
+                const int r0 = t * PULL_ROWS;
+                const int r1 = r0 + PULL_ROWS < a.n_recv_a ? r0 + PULL_ROWS : a.n_recv_a;
+                pull_rows(r0, r1, a.a_src, reinterpret_cast<float4*>(a.A_stage), ldb_v, a.nvec, lane);
+            } else {
+                const int r0 = (t - n_pull_a) * PULL_ROWS;
+                const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
+                pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
+            }
             __threadfence();
             __syncwarp();
             if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
             return true;
         };
-        // A warp alternates one pull ticket with work_per_pull compute tickets, so remote rows stream in
-        // while units that need none of them are computed.  Before it waits for the pulls it helps to
-        // finish them; hence every pull ticket is taken by a running warp and the wait cannot deadlock.
-        bool more = true;
+        // One warp in four is a puller: it serves pull tickets until none are left (a quarter of the warps,
+        // 4 KB of reads in flight each, is enough to fill NVLink) while the others start on the units that
+        // need no pulled row.  A warp that reaches a unit needing pulled rows first helps to finish the pulls
+        // and then waits for them; every pull ticket is thus taken by a running warp and the wait cannot
+        // deadlock.
+        const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+        if ((gwarp & 3) == 0 || n_free_units == 0)
+            while (ok && pulls_left) pulls_left = pull_one();
         const int SDDMM_UNITS_PER_TICKET = per_ticket(n_units, nwarps, SDDMM_UNITS_PER_TICKET_MAX);
-        while (ok && more) {
-            if (pulls_left) pulls_left = pull_one();
-            for (int w = 0; w < a.work_per_pull && ok; ++w) {
-                const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
-                if (u0 >= n_units) { more = false; break; }
-                const long long u1 = u0 + SDDMM_UNITS_PER_TICKET < n_units ? u0 + SDDMM_UNITS_PER_TICKET : n_units;
-                if (!pulled && u1 > n_free_units) {
-                    while (pulls_left) pulls_left = pull_one();
-                    ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
-                    pulled = true;
-                    if (!ok) break;
-                }
-                for (long long u = u0; u < u1; ++u)
-                    sddmm_warp_unit<float, G, R, U>(u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
+        while (ok) {
+            const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
+            if (u0 >= n_units) break;
+            const long long u1 = u0 + SDDMM_UNITS_PER_TICKET < n_units ? u0 + SDDMM_UNITS_PER_TICKET : n_units;
+            if (!pulled && u1 > n_free_units) {
+                while (pulls_left) pulls_left = pull_one();
+                ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
+                pulled = true;
+                if (!ok) break;
             }
+            for (long long u = u0; u < u1; ++u)
+                sddmm_warp_unit<float, G, R, U>(u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
         }
         while (ok && pulls_left) pulls_left = pull_one();  // no compute left but tiles remain (tiny blocks)
         if (a.Z > 1 && !direct) {

@@ -240,6 +240,15 @@ __global__ void touch_masks_kernel(long long nnz, const int* __restrict__ rows, 
     atomicOr(col_mask + c, 1ull << rowmap[r]);
 }
 
+// Debug check: every idx[i] lies in [0, limit); the first offender is recorded in the status words
+// {ST_BAD_INDEX, which, position, value} and nothing else happens (no trap).
+__global__ void check_range_kernel(long long n, const int* __restrict__ idx, int limit, int which, int* status) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int v = idx[i];
+    if (v < 0 || v >= limit) report(status, ST_BAD_INDEX, which, (int)i, v);
+}
+
 // ---- dispatch ---------------------------------------------------------------
 template <typename T>
 int launch_sddmm(long long nnz, const int* ri, const int* ci, const T* sv, const T* A, long long lda, const T* B,
@@ -382,6 +391,11 @@ SP3_API int sp3_cuda_sum_f32(const float* x, long long n, double* part, double* 
 SP3_API int sp3_cuda_sum_f64(const double* x, long long n, double* part, double* out, void* stream) {
     sum_stage1<double><<<1024, 256, 0, (cudaStream_t)stream>>>(x, n, part);
     sum_stage2<<<1, 256, 0, (cudaStream_t)stream>>>(part, 1024, out);
+    return (int)cudaGetLastError();
+}
+SP3_API int sp3_cuda_check_range(long long n, const int* idx, int limit, int which, int* status, void* stream) {
+    if (n == 0) return 0;
+    check_range_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, idx, limit, which, status);
     return (int)cudaGetLastError();
 }
 SP3_API int sp3_cuda_remap(long long n, const int* idx, const int* table, long long table_len, int* out,

@@ -29,6 +29,8 @@ src/distributed_comp.cpp:59; here it is defined by the math.)
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -73,6 +75,9 @@ class _Dist3DOp:
             colidx = self._dense_col.slab_index()[colidx].astype(np.int32)
         self.rowidx = torch.from_numpy(np.ascontiguousarray(rowidx)).to(self.device)
         self.colidx = torch.from_numpy(np.ascontiguousarray(colidx)).to(self.device)
+        if self.device.type == "cuda" and os.environ.get("SP3_DEBUG") == "1" and variant != "dense":
+            from ..ops import cuda_ops
+            cuda_ops.validate_indices(self.rowidx, self.colidx, plan.row.n_local, plan.col.n_local)
 
     # ---- helpers ---------------------------------------------------------
     def _alloc_local(self, side):

@@ -176,6 +176,20 @@ def new_status(device):
     return torch.zeros(4, dtype=torch.int32, device=device)
 
 
+def validate_indices(rowidx: torch.Tensor, colidx: torch.Tensor, nrows: int, ncols: int):
+    """Debug aid (the role compute-sanitizer would play): checks on the device
+    that all local row / column indices are in range and raises with the first
+    offender instead of letting a kernel read out of bounds."""
+    st = new_status(rowidx.device)
+    lib = native.cuda()
+    _ck(lib.sp3_cuda_check_range(rowidx.shape[0], native.ptr(rowidx), nrows, 0, native.ptr(st), _stream()), "check rows")
+    _ck(lib.sp3_cuda_check_range(colidx.shape[0], native.ptr(colidx), ncols, 1, native.ptr(st), _stream()), "check cols")
+    code, which, pos, val = st.tolist()
+    if code:
+        raise IndexError(f"{'row' if which == 0 else 'column'} index {val} at nonzero {pos} is outside "
+                         f"[0, {nrows if which == 0 else ncols})")
+
+
 def remap_indices(idx: torch.Tensor, table: torch.Tensor, status=None) -> torch.Tensor:
     out = torch.empty_like(idx)
     st = new_status(idx.device) if status is None else status

@@ -13,6 +13,7 @@ itself through NVLink peer addresses.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 import torch
@@ -43,7 +44,8 @@ class _SddmmArgs(C.Structure):
                 ("a_refs", P), ("a_bases", P), ("world", C.c_int), ("B_loc", P), ("ldb", C.c_longlong), ("n_owned_b", C.c_int),
                 ("n_recv_b", C.c_int), ("b_src", P), ("nvec", C.c_int), ("Z", C.c_int), ("my_z", C.c_int),
                 ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P),
-                ("part", P), ("direct_push", C.c_int), ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int)]
+                ("part", P), ("direct_push", C.c_int), ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int),
+                ("n_recv_a", C.c_int), ("a_src", P), ("A_stage", P)]
 
 
 class _SpmmLong(C.Structure):
@@ -192,24 +194,36 @@ class FusedSDDMM(_FusedBase):
         rb = k_loc * 4
         Z = plan.mesh.Z
         zwidth = plan.nnz // Z + (1 if plan.nnz % Z else 0)
-        return {"pad": F_KINDS * MAX_RANKS * 4, "A": plan.row.n_owned * rb, "B": plan.col.n_local * rb,
+        return {"pad": F_KINDS * MAX_RANKS * 4, "A": plan.row.n_local * rb, "B": plan.col.n_local * rb,
                 "zbuf": 2 * Z * zwidth * 4 if Z > 1 else 0}
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
-                 overlap: bool = True, direct_push: bool | None = None):
+                 overlap: bool = True, direct_push: bool | None = None, stage_a: bool | None = None):
         super().__init__(op, heap, fabric, timeout_s)
         p, h, k = self.plan, self.heap, self.k_loc
         Z, z = p.mesh.Z, p.coords[2]
-        # A: only my owned rows live here (peers read them in place); the op's A_loc is that block
-        self.A_loc = h.view("A", torch.float32, (p.row.n_owned, k))
+        # A block: my owned rows (peers read them in place) followed by room for staged copies of the remote
+        # rows I need.  Default: every remote A row is read straight from its owner when a work unit first
+        # needs it (measured equal or faster on 2 GPUs: 0.458 vs 0.475 ms, R-MAT-20, 1x2x1); stage_a pulls
+        # them in bulk like the B rows instead.
+        if stage_a is None:
+            stage_a = os.environ.get("SP3_FUSED_STAGE_A", "0") == "1"
+        self.stage_a = bool(stage_a)
+        self._A_full = h.view("A", torch.float32, (p.row.n_local, k))
+        self.A_loc = self._A_full[:p.row.n_owned]
         self.B_loc = h.view("B", torch.float32, (p.col.n_local, k))
         _, b_need = self._side_tables(p.col, "B")
         # A rows stay where they are: reference = owner rank << 25 | row inside the owner's block
         if max(int(p.row.peer_owned.max(initial=0)), p.row.n_owned) >= 1 << 25:
             raise ValueError("more than 2^25 owned rows on one rank")
         row_ranks = np.asarray(_peer_ranks(p, "row"), dtype=np.int64)
-        refs = np.concatenate([(self.rank << 25) | np.arange(p.row.n_owned, dtype=np.int64),
-                               (row_ranks[p.row.recv_peer] << 25) | p.row.recv_src_idx.astype(np.int64)])
+        if self.stage_a:
+            refs = (self.rank << 25) | np.arange(p.row.n_local, dtype=np.int64)
+        else:
+            refs = np.concatenate([(self.rank << 25) | np.arange(p.row.n_owned, dtype=np.int64),
+                                   (row_ranks[p.row.recv_peer] << 25) | p.row.recv_src_idx.astype(np.int64)])
+        _, a_need = self._side_tables(p.row, "A")
+        self.a_src = self._dev_i64(a_need if a_need.size else [0])
         self.a_refs = self._dev_i32(refs if refs.size else [0])
         self.a_bases = self._dev_i64([h.addr("A", r) for r in range(h.world)])
         self.b_src = self._dev_i64(b_need if b_need.size else [0])
@@ -229,8 +243,13 @@ class FusedSDDMM(_FusedBase):
         a.nnz = p.nnz
         # nonzeros whose B row is owned first (computable while the pulls are in flight), the others after
         # them; both parts keep the row-sorted order, results are stored at their position in the plan's order
-        if overlap and p.col.n_recv > 0 and p.nnz > 0:
+        n_recv_a = p.row.n_recv if self.stage_a else 0
+        a.n_recv_a, a.a_src = n_recv_a, self.a_src.data_ptr()
+        a.A_stage = self._A_full.data_ptr() + p.row.n_owned * self.row_bytes
+        if overlap and (p.col.n_recv + n_recv_a) > 0 and p.nnz > 0:
             needs_pull = p.colidx >= p.col.n_owned
+            if self.stage_a:
+                needs_pull = needs_pull | (p.rowidx >= p.row.n_owned)
             order = np.argsort(needs_pull, kind="stable")
             nnz_free = int(p.nnz - needs_pull.sum())
             self._perm = (self._dev_i32(p.rowidx[order]), self._dev_i32(p.colidx[order]),
@@ -239,7 +258,7 @@ class FusedSDDMM(_FusedBase):
             a.rowidx, a.colidx, a.sval, a.orig = (t.data_ptr() for t in self._perm)
             a.nnz_free = nnz_free
             nnz_per_ticket = 4 * 64  # a few units of 32..64 nonzeros (the kernel sizes tickets itself)
-            n_pull = -(-p.col.n_recv // 64)
+            n_pull = -(-p.col.n_recv // 64) + -(-n_recv_a // 64)
             a.work_per_pull = max(1, min(64, (nnz_free // nnz_per_ticket) // max(1, n_pull)))
         else:
             a.rowidx, a.colidx, a.sval = op.rowidx.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()

@@ -53,6 +53,7 @@ class PhaseTimer:
 
         def __enter__(self):
             if self.t.cuda:
+                torch.cuda.nvtx.range_push(f"sp3:{self.name}")
                 self.a = torch.cuda.Event(enable_timing=True)
                 self.b = torch.cuda.Event(enable_timing=True)
                 self.a.record()
@@ -63,6 +64,7 @@ class PhaseTimer:
         def __exit__(self, *exc):
             if self.t.cuda:
                 self.b.record()
+                torch.cuda.nvtx.range_pop()
                 self.t._pending.append((self.name, self.a, self.b))
             else:
                 self.t.ms[self.name] = self.t.ms.get(self.name, 0.0) + (time.perf_counter() - self.t0) * 1e3

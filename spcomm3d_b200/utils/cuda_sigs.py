@@ -15,6 +15,7 @@ CUDA_SIGS = {
     "sp3_cuda_fill_rows_f64": ("int", _FILL),
     "sp3_cuda_sum_f32": ("int", "p i64 p p p"),
     "sp3_cuda_sum_f64": ("int", "p i64 p p p"),
+    "sp3_cuda_check_range": ("int", "i64 p int int p p"),
     "sp3_cuda_remap": ("int", "i64 p p i64 p p p"),
     "sp3_cuda_invert_perm": ("int", "i64 p p p p"),
     "sp3_cuda_touch_masks": ("int", "i64 p p p p p p p"),

@@ -212,3 +212,12 @@ def test_sddmm_dense_panels_on_tensor_cores(k):
     # the remainder went through the fp32 kernel and is tight
     rest = op.r_pos.cpu().long()
     assert err[rest].max() <= 2e-5 * max(1.0, ref.abs().max()) * k ** 0.5
+
+
+def test_validate_indices_reports_instead_of_faulting():
+    from spcomm3d_b200.ops import cuda_ops
+    r = torch.tensor([0, 1, 2, 3], dtype=torch.int32, device="cuda")
+    c = torch.tensor([0, 5, 9, 2], dtype=torch.int32, device="cuda")
+    cuda_ops.validate_indices(r, c, 4, 10)
+    with pytest.raises(IndexError, match="column index 9 at nonzero 2"):
+        cuda_ops.validate_indices(r, c, 4, 9)

@@ -40,7 +40,7 @@ def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap):
     kl = [split_k(k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
     heaps = fabric.heaps([FusedSDDMM.region_sizes(plans[r], kl[r]) for r in range(mesh.size)])
     ops = [DistSDDMM(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0,
-                     overlap=overlap, direct_push=overlap)
+                     overlap=overlap, direct_push=overlap, stage_a=not overlap)
            for r in range(mesh.size)]
     for epoch in range(2):
         for op in ops:
