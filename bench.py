@@ -194,7 +194,7 @@ def run_ours(args):
         b.record()
         barrier()
         e2e_ms = maxr(a.elapsed_time(b)) / args.steps
-        e2e = {"value": e2e_ms, "unit": "ms/iter (SDDMM+SpMM, incl. H2D operands + D2H checksums)",
+        e2e = {"value": e2e_ms, "unit": "ms/iter (SDDMM+SpMM, incl. H2D of A and B from pinned memory + D2H of the two checksums)",
                "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes,
                "checksums": [float(x) for x in res]}
 

@@ -64,19 +64,20 @@ class SddmmSpmmStep:
     @property
     def h2d_bytes(self):
         h = self.host
-        return int(h["A"].numel() * h["A"].element_size() + 2 * h["B"].numel() * h["B"].element_size())
+        return int(h["A"].numel() * h["A"].element_size() + h["B"].numel() * h["B"].element_size())
 
     @property
     def d2h_bytes(self):
         return 16
 
     def run_e2e(self):
-        """Copies A, B and X from host memory, runs SDDMM then SpMM and reads
+        """Copies the step's inputs A and B from pinned host memory (X of the
+        SpMM is B: one device-to-device copy), runs SDDMM then SpMM and reads
         back the checksums of this rank's results (two fp64 scalars)."""
         sd, sp, h = self.sddmm, self.spmm, self.host
         sd.A_owned.copy_(h["A"], non_blocking=True)
         sd.B_owned.copy_(h["B"], non_blocking=True)
-        sp.X_owned.copy_(h["B"], non_blocking=True)
+        sp.X_owned.copy_(sd.B_owned)
         c = sd.run_async()
         y = sp.run_async()
         if self.device.type == "cuda":
