@@ -41,7 +41,9 @@ def run(args):
     tmp = Path(os.environ.get("TMPDIR", "/tmp")) / f"sp3_ref_{job}"
     ready, failed = tmp / "READY", tmp / "FAILED"
     steps, warmup = min(args.steps, MAX_STEPS), min(args.warmup, MAX_WARMUP)
-    Z = int(args.mesh.lower().split("x")[2]) if args.mesh else (2 if world % 2 == 0 else 1)
+    # same Z as our arm's default mesh; the reference then balances X >= Y itself (MPI_Dims_create)
+    default_z = {1: 1, 2: 1, 4: 1, 8: 2}.get(world, 2 if world % 2 == 0 else 1)
+    Z = int(args.mesh.lower().split("x")[2]) if args.mesh else default_z
     binpath = tmp / "matrix.bin"
     if rank == 0:
         try:

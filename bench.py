@@ -38,7 +38,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gen", default="rmat:22:16", help="matrix spec (utils.generate.from_spec)")
     ap.add_argument("--k", type=int, default=128)
-    ap.add_argument("--mesh", default=None, help="XxYxZ (default: balanced X>=Y with Z=2 when N is even)")
+    ap.add_argument("--mesh", default=None, help="XxYxZ (default: the fastest measured mesh for N = 2, 4, 8)")
     ap.add_argument("--variant", default=None, choices=[None, "fused", "sparse", "sparseNRB", "dense"])
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
@@ -46,6 +46,19 @@ def parse_args():
                     help="SDDMM: dense 128x64 panels on the tcgen05 tensor cores (TF32), rest on the gather kernel")
     ap.add_argument("--min-col-nnz", type=int, default=3)
     return ap.parse_args()
+
+
+# Fastest mesh per GPU count among those measured on this matrix (fused variant, SDDMM + SpMM):
+# N=2: 1x2x1 1.07 ms vs 2x1x1 1.17, 1x1x2 1.23 (R-MAT-20); N=4: 2x2x1 2.49 ms vs 1x2x2 2.70, 2x1x2 2.94;
+# N=8: 2x2x2 1.99 ms vs 4x2x1 2.05 (R-MAT-22).
+MEASURED_MESH = {1: (1, 1, 1), 2: (1, 2, 1), 4: (2, 2, 1), 8: (2, 2, 2)}
+
+
+def default_mesh(world: int):
+    if world in MEASURED_MESH:
+        return MEASURED_MESH[world]
+    from spcomm3d_b200.parallel.mesh import dims_create
+    return dims_create(world, 2 if world % 2 == 0 else 1)
 
 
 class ClockSampler:
@@ -128,7 +141,7 @@ def run_ours(args):
     groups = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    mesh = Mesh3D.parse(args.mesh) if args.mesh else Mesh3D(*dims_create(world, 2 if world % 2 == 0 else 1))
+    mesh = Mesh3D.parse(args.mesh) if args.mesh else Mesh3D(*default_mesh(world))
     if mesh.size != world:
         raise SystemExit(f"mesh {mesh} does not match {world} ranks")
     if world > 1:

@@ -41,4 +41,4 @@ def test_reference_arm_four_ranks_under_torchrun():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-2000:]
     d = _last_json(out.stdout)
-    assert d["n_gpus"] == 4 and d["config"]["mesh"] == "2x1x2" and d["sddmm_ms"] > 0 and d["spmm_ms"] > 0
+    assert d["n_gpus"] == 4 and d["config"]["mesh"] == "2x2x1" and d["sddmm_ms"] > 0 and d["spmm_ms"] > 0
