@@ -260,10 +260,16 @@ __device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long
     using V = typename Vec<T>::type;
     constexpr int UU = U < G ? U : G;
     if (r0 >= r1) return;
-    const long long qend = rowptr[r1];
-    long long base = rowptr[r0];
+    // positions are kept as 32-bit offsets from the first nonzero of the range (an item holds far fewer
+    // than 2^31 nonzeros); the dense-row stride is a 32-bit factor so that a row address costs one wide multiply
+    const long long q0 = rowptr[r0];
+    const int* __restrict__ cix = colidx + q0;
+    const T* __restrict__ vls = val + q0;
+    const int qend = (int)(rowptr[r1] - q0);
+    const int ld = (int)ldx_v;
+    int base = 0;
     int row = r0;
-    long long row_end = rowptr[r0 + 1];
+    int row_end = (int)(rowptr[r0 + 1] - q0);
     V acc[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r] = vzero((V*)nullptr);
@@ -275,21 +281,21 @@ __device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long
             acc[r] = vzero((V*)nullptr);
         }
     };
-    int nxt_c = (base + gl < qend) ? __ldg(colidx + base + gl) : -1;
-    T nxt_v = (base + gl < qend) ? __ldg(val + base + gl) : (T)0;
+    int nxt_c = (gl < qend) ? __ldg(cix + gl) : -1;
+    T nxt_v = (gl < qend) ? __ldg(vls + gl) : (T)0;
     while (base < qend) {
         const int my_c = nxt_c;
         const T my_v = nxt_v;
-        const long long nb = base + G;
-        nxt_c = (nb + gl < qend) ? __ldg(colidx + nb + gl) : -1;
-        nxt_v = (nb + gl < qend) ? __ldg(val + nb + gl) : (T)0;
-        const int n = (qend - base) < G ? (int)(qend - base) : G;
+        const int nb = base + G;
+        nxt_c = (nb + gl < qend) ? __ldg(cix + nb + gl) : -1;
+        nxt_v = (nb + gl < qend) ? __ldg(vls + nb + gl) : (T)0;
+        const int n = (qend - base) < G ? (qend - base) : G;
         for (int j = 0; j < n; j += UU) {
             int cc[UU];
             T vv[UU];
 #pragma unroll
             for (int u = 0; u < UU; ++u) {
-                cc[u] = __shfl_sync(gmask, my_c, j + u, G);
+                cc[u] = __shfl_sync(gmask, my_c, j + u, G);  // -1 past the end of the range
                 vv[u] = __shfl_sync(gmask, my_v, j + u, G);
             }
             V x[UU][R];
@@ -298,16 +304,16 @@ __device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int v = gl + r * G;
-                    x[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Xv + (long long)cc[u] * ldx_v + v) : vzero((V*)nullptr);
+                    x[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Xv + (long long)cc[u] * ld + v) : vzero((V*)nullptr);
                 }
 #pragma unroll
             for (int u = 0; u < UU; ++u) {
-                if (j + u < n) {
-                    const long long q = base + j + u;
+                if (cc[u] >= 0) {
+                    const int q = base + j + u;
                     while (q >= row_end) {
                         flush(row);
                         ++row;
-                        row_end = rowptr[row + 1];
+                        row_end = (int)(rowptr[row + 1] - q0);
                     }
 #pragma unroll
                     for (int r = 0; r < R; ++r) vfma(acc[r], vv[u], x[u][r]);
@@ -322,12 +328,6 @@ __device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long
     }
 }
 
-// One work item of the SpMM schedule, processed by one warp.
-//   rows item   {row_begin, row_end, 0, -1}: lane groups split the rows.
-//   piece item  {row, nnz_begin, nnz_end, long_row_slot}: a slice of a long
-//               row; the warp's partial goes to the carry scratch and the
-//               warp that completes the row adds the pieces in piece order
-//               (fixed order => bitwise reproducible) and emits the row.
 template <typename T, int G, int R, int U, typename Emit>
 __device__ __forceinline__ void spmm_warp_item(const int4 item, const long long* __restrict__ rowptr,
                                                const int* __restrict__ colidx, const T* __restrict__ val,
