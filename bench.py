@@ -65,7 +65,7 @@ class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML (read
     only) while the timed region runs."""
 
-    def __init__(self, index: int, period=0.1):
+    def __init__(self, index: int, period=0.004):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
