@@ -38,8 +38,7 @@ def main(argv=None):
                     stats.report_iteration(op, rt.groups, rt.rank)
                 del op
         if args.chain:
-            layer = GatLayer(plan, rt.groups, k, rt.dtype, rt.device,
-                             "sparseNRB" if sparse_variant == "fused" else sparse_variant)
+            layer = GatLayer(plan, rt.groups, k, rt.dtype, rt.device, sparse_variant)
             layer.sddmm.fill_owned(layer.sddmm.A_owned, plan.row.owned_gids, seed=args.seed, stream=1)
             layer.sddmm.fill_owned(layer.sddmm.B_owned, plan.col.owned_gids, seed=args.seed, stream=2)
             layer.spmm.fill_owned(layer.spmm.X_owned, plan.col.owned_gids, seed=args.seed, stream=2)

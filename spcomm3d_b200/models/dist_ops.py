@@ -132,7 +132,8 @@ class DistSDDMM(_Dist3DOp):
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSDDMM
-            self._fused = FusedSDDMM(self, **kw)
+            self._fused = FusedSDDMM(self, **{k_: v for k_, v in kw.items() if k_ in (
+                "heap", "fabric", "timeout_s", "overlap", "direct_push", "stage_a")})
             self.A_loc, self.B_loc = self._fused.A_loc, self._fused.B_loc
         else:
             self.A_loc, self.B_loc = self._alloc_local(p.row), self._alloc_local(p.col)
@@ -210,7 +211,7 @@ class DistSpMM(_Dist3DOp):
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSpMM
-            self._fused = FusedSpMM(self, **kw)
+            self._fused = FusedSpMM(self, **{k_: v for k_, v in kw.items() if k_ in ("heap", "fabric", "timeout_s")})
             self.X_loc, self.Y_loc = self._fused.X_loc, self._fused.Y_loc
         else:
             self.X_loc, self.Y_loc = self._alloc_local(p.col), self._alloc_local(p.row)

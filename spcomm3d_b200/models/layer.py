@@ -102,10 +102,10 @@ class SddmmSpmmStep:
 class GatLayer:
     """Y = (S o (A B^T)) X on the mesh; returns owned rows of Y."""
 
-    def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB"):
+    def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
         self.plan, self.groups = plan, groups
-        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant)
-        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant)
+        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant, **kw)
+        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant, **kw)
         Z = plan.mesh.Z
         self.slices = [split_nnz(plan.nnz, Z, z) for z in range(Z)]
         self.width = self.slices[0][1]

@@ -53,6 +53,22 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
             if yref.numel():
                 err = (y.cpu().double() - yref).abs().max()
                 assert err <= 2e-5 * max(1.0, yref.abs().max()) * 8, (variant, "spmm", float(err))
+    # attention-style chain on the fused kernels: Y = (S o (A B^T)) X with X = B
+    from spcomm3d_b200.models.layer import GatLayer
+    layer = GatLayer(plan, groups, k, torch.float32, dev, "fused", fabric=fabric, timeout_s=10.0)
+    A = generate.fill_rows(np.arange(m.nrows), k, 0, k, seed=5, stream=1, dtype=np.float64)
+    B = generate.fill_rows(np.arange(m.ncols), k, 0, k, seed=5, stream=2, dtype=np.float64)
+    layer.sddmm.fill_owned(layer.sddmm.A_owned, plan.row.owned_gids, seed=5, stream=1)
+    layer.sddmm.fill_owned(layer.sddmm.B_owned, plan.col.owned_gids, seed=5, stream=2)
+    layer.spmm.fill_owned(layer.spmm.X_owned, plan.col.owned_gids, seed=5, stream=2)
+    y = layer.run()
+    scores = oracle.sddmm_ref(m, A, B)
+    cm = CooMatrix(m.nrows, m.ncols, m.rows, m.cols, scores.numpy())
+    ko, kw_ = split_k(k, mesh.Z, plan.coords[2])
+    yref = oracle.spmm_ref(cm, B)[plan.row.owned_gids][:, ko:ko + kw_]
+    if yref.numel():
+        err = (y.cpu().double() - yref).abs().max()
+        assert err <= 1e-4 * max(1.0, yref.abs().max()) * 8, ("chain", float(err))
     fabric.close()
 
 
