@@ -238,7 +238,9 @@ struct FusedSddmmArgs {
     float* out;                   // my slice of C
     float* part;                  // [nnz] local partial values (used when Z > 1)
     int direct_push;              // 1: values of other fiber ranks are stored remotely as they are computed;
-                                  // 0: they are staged in `part` and pushed in bulk (narrow rows)
+                                  // 0: they are staged in `part` and pushed in bulk once all are there;
+                                  // 2: staged, and every warp pushes the range of a ticket right after computing
+                                  //    it (needs orig == null: a ticket's values are then one contiguous range)
     // Overlap of pulls and compute: the kernel walks the nonzeros in the order "those whose B row is owned
     // first, then those that need a pulled row" (rowidx / colidx / sval are given in that order);
     // orig[i] is the position of nonzero i in the plan's value order (null: identity), nnz_free the
@@ -303,7 +305,8 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         const long long per_unit = (long long)SLOTS * SDDMM_PER_SLOT;
         const long long n_units = (a.nnz + per_unit - 1) / per_unit;
         const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull};
-        const int direct = a.Z > 1 && a.direct_push;
+        const int direct = a.Z > 1 && a.direct_push == 1;
+        const bool self_push = a.Z > 1 && a.direct_push == 2 && a.orig == nullptr;
         const StorePartial store{a.sval, a.orig, a.Z > 1 ? a.part : a.out, a.zbuf, direct, a.Z, a.my_z, parity,
                                  a.zbase, a.zrem, a.zwidth};
         float4* Bv = reinterpret_cast<float4*>(a.B_loc);
@@ -348,9 +351,30 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
             }
             for (long long u = u0; u < u1; ++u)
                 sddmm_warp_unit<float, G, R, U>(u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
+            if (self_push) {
+                // the values [i0, i1) of `part` were written by this warp just now (still in L2): send the pieces
+                // that belong to other fiber ranks as contiguous remote stores while other warps compute
+                __syncwarp();
+                const long long i0 = u0 * per_unit, i1 = u1 * per_unit < a.nnz ? u1 * per_unit : a.nnz;
+                for (int z = 0; z < a.Z; ++z) {
+                    if (z == a.my_z) continue;
+                    const long long s0 = slice_off(z, a.zbase, a.zrem);
+                    const long long s1 = s0 + a.zbase + ((unsigned)z < a.zrem ? 1 : 0);
+                    const long long j0 = i0 > s0 ? i0 : s0, j1 = i1 < s1 ? i1 : s1;
+                    if (j0 >= j1) continue;
+                    float* dst = a.zbuf[z] + ((long long)parity * a.Z + a.my_z) * a.zwidth - s0;
+                    for (long long j = j0 + lane; j < j1; j += 128) {
+                        float v[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) v[q] = (j + 32 * q < j1) ? __ldcg(a.part + j + 32 * q) : 0.f;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) if (j + 32 * q < j1) __stcs(dst + j + 32 * q, v[q]);
+                    }
+                }
+            }
         }
         while (ok && pulls_left) pulls_left = pull_one();  // no compute left but tiles remain (tiny blocks)
-        if (a.Z > 1 && !direct) {
+        if (a.Z > 1 && !direct && !self_push) {
             // all partial values of this rank are in `part` once every warp has passed this point; then the
             // slices of the other fiber ranks travel as contiguous, fully coalesced remote stores
             __threadfence();

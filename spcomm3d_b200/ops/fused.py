@@ -275,8 +275,18 @@ class FusedSDDMM(_FusedBase):
         a.out = self.out.data_ptr()
         self.part = torch.zeros(p.nnz if Z > 1 else 1, dtype=torch.float32, device=self.device)
         a.part = self.part.data_ptr()
-        # a lane group stores (k_loc/8) consecutive values at a time: direct remote stores only pay for >= 32 bytes
-        a.direct_push = int(direct_push if direct_push is not None else k >= 64)
+        # Push mode of the partial values (Z > 1).  1: remote stores as the values are computed -- a lane group
+        # stores (k_loc/8) consecutive values at a time, which only pays for >= 32 bytes; 0: staged in `part`,
+        # pushed in bulk after all of them are there; 2: staged, every warp pushes the contiguous range of its
+        # ticket right after computing it (only without the reordering for pull/compute overlap).
+        if direct_push is None and "SP3_FUSED_PUSH" in os.environ:
+            direct_push = int(os.environ["SP3_FUSED_PUSH"])
+        if direct_push is None:
+            direct_push = 1 if k >= 64 else (2 if not a.orig else 0)
+        direct_push = int(direct_push)
+        if direct_push == 2 and a.orig:
+            direct_push = 0
+        a.direct_push = self.push_mode = direct_push
 
     def launch(self, phases=PH_ALL, new_epoch=True):
         if new_epoch:

@@ -25,10 +25,12 @@ def _setup(meshstr, gen, k, seed=3):
 MESHES = ["2x2x2", "4x2x1", "1x1x8", "2x1x2", "1x2x1", "3x2x1"]
 
 
-@pytest.mark.parametrize("overlap", [True, False])
+# (pull/compute overlap, push mode of the Z partials: 1 direct, 0 staged + bulk, 2 staged + per-ticket, staged A rows)
+@pytest.mark.parametrize("overlap,push,stage_a", [(True, 1, False), (False, 0, True), (False, 2, False),
+                                                  (True, None, False)])
 @pytest.mark.parametrize("meshstr", MESHES)
 @pytest.mark.parametrize("gen,k", [("uniform:600:500:7", 64), ("zipf:700:900:1.6:600", 32)])
-def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap):
+def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap, push, stage_a):
     from spcomm3d_b200.models.dist_ops import DistSDDMM
     from spcomm3d_b200.ops import oracle
     from spcomm3d_b200.ops.fused import FusedSDDMM, run_lockstep
@@ -40,7 +42,7 @@ def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap):
     kl = [split_k(k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
     heaps = fabric.heaps([FusedSDDMM.region_sizes(plans[r], kl[r]) for r in range(mesh.size)])
     ops = [DistSDDMM(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0,
-                     overlap=overlap, direct_push=overlap, stage_a=not overlap)
+                     overlap=overlap, direct_push=push, stage_a=stage_a)
            for r in range(mesh.size)]
     for epoch in range(2):
         for op in ops:
