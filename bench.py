@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--panels", action="store_true",
-                    help="SDDMM: dense 128x64 panels on the tcgen05 tensor cores (TF32), rest on the gather kernel")
+                    help="SDDMM and SpMM: dense 128x64 panels on the tcgen05 tensor cores (TF32), rest on the gather kernels")
     ap.add_argument("--min-col-nnz", type=int, default=3)
     return ap.parse_args()
 
@@ -227,7 +227,7 @@ def run_ours(args):
                                 "spmm_expand": vol_t[2].item(), "spmm_reduce": vol_t[3].item()},
         "gpu_launches": launches, "clocks": clocks.summary(), "e2e": e2e,
         "config": {"model": f"{args.gen} k={args.k} fp32 SDDMM then SpMM", "matrix": args.gen, "nnz": gnnz,
-                   "k": args.k, "mesh": str(mesh), "variant": variant, "sddmm_precision": "tf32 panels + fp32" if args.panels else "fp32", "global_batch": None, "seq_len": None,
+                   "k": args.k, "mesh": str(mesh), "variant": variant, "precision": "tf32 panels + fp32" if args.panels else "fp32", "global_batch": None, "seq_len": None,
                    "parallelism": f"mesh{mesh}", "l2": "operands larger than L2 at every N; no flush",
                    "setup_s": round(setup_s, 1)},
     }

@@ -245,6 +245,13 @@ class DistSpMM(_Dist3DOp):
                 self._d_sched = cuda_ops.SpmmSchedule(self._d_rowptr)
             else:
                 self.sched = cuda_ops.SpmmSchedule(self.rowptr)
+        # opt-in: dense (128-row x 64-column) panels of S as TF32 products on the tensor cores
+        self._panels = None
+        if (kw.get("panels") and variant in ("sparse", "sparseNRB") and self.device.type == "cuda"
+                and dtype == torch.float32 and self.k_loc % 32 == 0 and self.k_loc <= 256):
+            from ..ops.panel import PanelSpMM
+            self._panels = PanelSpMM(p.rowidx, p.colidx, p.vals, p.row.n_local, p.col.n_local, self.device,
+                                     **{k_: v for k_, v in kw.items() if k_ in ("min_col_nnz", "min_panel_nnz")})
 
     def _local_buffers(self):
         return [(self.X_loc, self.plan.col)]
@@ -273,8 +280,11 @@ class DistSpMM(_Dist3DOp):
             with t.span("comm1"):
                 self.exX.expand(self.X_loc)
             with t.span("comp"):
-                local.spmm(self.rowptr, self.rowidx, self.colidx, self.vals, self.X_loc, self.Y_loc, 0.0,
-                           self.sched)
+                if self._panels is not None:
+                    self._panels.run(self.X_loc, self.Y_loc, 0.0)
+                else:
+                    local.spmm(self.rowptr, self.rowidx, self.colidx, self.vals, self.X_loc, self.Y_loc, 0.0,
+                               self.sched)
             with t.span("comm2"):
                 self.exY.reduce(self.Y_loc)  # adds the peers' partial rows into the owned head = Y_owned
                 if prev is not None:

@@ -24,11 +24,11 @@ STREAM_A, STREAM_B = 1, 2
 
 class SddmmSpmmStep:
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cuda", variant="sparseNRB", seed=0,
-                 **sddmm_kw):
+                 **kw):
         self.plan, self.k, self.seed = plan, k, seed
         self.device = torch.device(device)
-        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant, **sddmm_kw)
-        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant)
+        self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant, **kw)
+        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant, **kw)
         self.host = None
 
     def fill_device_operands(self):
@@ -105,7 +105,9 @@ class GatLayer:
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
         self.plan, self.groups = plan, groups
         self.sddmm = DistSDDMM(plan, groups, k, dtype, device, variant, **kw)
-        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant, **kw)
+        # the SpMM values change every run (they are the SDDMM scores): no precomputed value panels here
+        self.spmm = DistSpMM(plan, groups, k, dtype, device, variant,
+                             **{k_: v for k_, v in kw.items() if k_ != "panels"})
         Z = plan.mesh.Z
         self.slices = [split_nnz(plan.nnz, Z, z) for z in range(Z)]
         self.width = self.slices[0][1]

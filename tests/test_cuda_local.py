@@ -214,6 +214,39 @@ def test_sddmm_dense_panels_on_tensor_cores(k):
     assert err[rest].max() <= 2e-5 * max(1.0, ref.abs().max()) * k ** 0.5
 
 
+@pytest.mark.parametrize("k", [32, 64, 128, 256])
+def test_spmm_dense_panels_on_tensor_cores(k):
+    """Panels of a hub block accumulate S_panel @ X in TMEM (tcgen05 TF32); remainder + beta via the gather kernel."""
+    from spcomm3d_b200.ops.panel import PanelSpMM
+    rng = np.random.default_rng(6)
+    nrows, ncols = 1000, 900
+    hub_cols = rng.choice(ncols, 150, replace=False)   # three 64-column tiles per block, the last one partial
+    rr, cc = np.nonzero(rng.random((300, 150)) < 0.3)  # rows 256..299: a block whose last rows hold no panel nonzeros
+    rows = np.concatenate([rr, rng.integers(0, nrows, 6000)])
+    cols = np.concatenate([hub_cols[cc], rng.integers(0, ncols, 6000)])
+    keys = np.unique(rows.astype(np.int64) * ncols + cols)
+    rows, cols = (keys // ncols).astype(np.int32), (keys % ncols).astype(np.int32)
+    vals = rng.random(keys.size)
+    X = torch.from_numpy(rng.standard_normal((ncols, k))).float()
+    Y0 = torch.from_numpy(rng.standard_normal((nrows, k))).float()
+    S = torch.sparse_coo_tensor(np.stack([rows, cols]).astype(np.int64), torch.from_numpy(vals), (nrows, ncols))
+    # group_panels = 8: one group per row block (plain stores); 2: hub blocks cut into groups (atomic adds)
+    for group_panels, beta in ((8, 0.0), (8, 0.5), (2, 0.5)):
+        op = PanelSpMM(rows, cols, vals, nrows, ncols, group_panels=group_panels)
+        assert op.npanels >= 4 and op.n_panel_nnz > 5000 and op.n_panel_nnz + op.n_rest == keys.size
+        assert (op.ngroups > 3 and int(op.grp_shared.sum()) > 0) if group_panels == 2 else int(op.grp_shared.sum()) == 0
+        Y = Y0.clone().cuda()
+        op.run(X.cuda(), Y, beta)
+        torch.cuda.synchronize()
+        assert op.status.tolist()[0] == 0, op.status.tolist()
+        ref = beta * Y0.double() + torch.sparse.mm(S, X.double())
+        err = (Y.cpu().double() - ref).abs()
+        assert not torch.isnan(Y).any()
+        # TF32 operands: ~2^-11 relative per product; a hub row sums ~45 panel products of size <= 1 * |x|
+        assert err.max() <= 2e-2
+        # rows without panel nonzeros went through the fp32 kernel only and are tight
+        assert err[600:].max() <= 2e-5 * max(1.0, float(ref.abs().max()))
+
 def test_validate_indices_reports_instead_of_faulting():
     from spcomm3d_b200.ops import cuda_ops
     r = torch.tensor([0, 1, 2, 3], dtype=torch.int32, device="cuda")
