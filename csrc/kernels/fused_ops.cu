@@ -46,7 +46,7 @@ namespace sp3 {
 
 constexpr int MAX_RANKS = 64;
 enum FlagKind : int { F_READY = 0, F_DONE = 1, F_PART = 2, F_KINDS = 3 };
-enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_TICKET_WORK = 6, C_WORK_DONE = 7, C_TICKET_PUSH = 8, C_WORDS = 16 };
+enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_TICKET_WORK = 6, C_WORK_DONE = 7, C_TICKET_PUSH = 8, C_TICKET_START = 9, C_START_DONE = 10, C_WORDS = 16 };
 enum Phase : int { PH_START = 1, PH_MAIN = 2, PH_FINISH = 4 };
 enum WaitSite : int { W_READY = 1, W_PULLS = 2, W_PART = 3, W_DONE = 4, W_WORK = 5 };
 
@@ -456,6 +456,14 @@ struct FusedSpmmArgs {
     const int* cslot;             // slot row of each contribution, ascending source rank
     const float* slots;           // my slot buffer (parity 0)
     long long lds;
+    // Atomic mode (no slots, no ordered sum): Y lives in the symmetric heap, y_dst holds the address of every
+    // row I do not own inside its owner's Y, partial rows are added there with atomics.  The START phase scales
+    // the owned rows that receive contributions by beta and only then signals READY; those rows (crow_flag) are
+    // updated with atomics by their owner too.  Results depend on the order of the additions (not bitwise
+    // reproducible).
+    int atomic;
+    int red_v4;                   // 1: 16-byte vector atomics also for remote rows, 0: one 4-byte atomic per value
+    const unsigned char* crow_flag;  // [n_owned_y] 1: row receives contributions from peers
 };
 
 // Rows I own go straight into the result (Y = beta*Y + my partial; the owners' FINISH phase then adds what
@@ -476,16 +484,71 @@ struct EmitOwnedOrPush {
     }
 };
 
-template <int G, int R, int U>
+// Atomic mode of the same routing: see FusedSpmmArgs::atomic.
+struct EmitOwnedOrAdd {
+    float4* Yv;
+    long long ldy_v;
+    float beta;
+    int n_owned;
+    float4* const* y_dst;
+    const unsigned char* crow_flag;
+    int red_v4;
+    __device__ __forceinline__ void operator()(int row, int v, const float4& acc) const {
+        if (row < n_owned) {
+            float4* y = Yv + (long long)row * ldy_v + v;
+            if (__ldg(crow_flag + row)) atomicAdd(y, acc);  // beta was applied in the START phase
+            else if (beta != 0.f) { float4 o = vscale(beta, *y); vadd(o, acc); *y = o; }
+            else *y = acc;
+        } else {
+            float4* y = ldg_ptr(y_dst + (row - n_owned)) + v;
+            if (red_v4) atomicAdd(y, acc);
+            else {
+                float* f = reinterpret_cast<float*>(y);
+                atomicAdd(f, acc.x); atomicAdd(f + 1, acc.y); atomicAdd(f + 2, acc.z); atomicAdd(f + 3, acc.w);
+            }
+        }
+    }
+};
+
+template <int G, int R, int U, bool ATOMIC>
 __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) {
     const FusedComm& c = a.comm;
     const int lane = threadIdx.x & 31;
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
-    if (c.phases & PH_START) start_phase(c);
+    if ((c.phases & PH_START) && !ATOMIC) start_phase(c);
+    if ((c.phases & PH_START) && ATOMIC) {
+        // scale the rows that peers will add to, then tell readers and contributors that this rank is ready
+        if (blockIdx.x == 0 && threadIdx.x == 0) stamp(c, T_START);
+        const int n_chunks = (a.n_crows + REDUCE_ROWS - 1) / REDUCE_ROWS;
+        float4* Yv = reinterpret_cast<float4*>(a.Y);
+        const long long ldy_v = a.ldy / 4;
+        for (;;) {
+            const int t = warp_ticket(c.ctrl + C_TICKET_START, lane);
+            if (t >= n_chunks) break;
+            const int r0 = t * REDUCE_ROWS;
+            const int r1 = r0 + REDUCE_ROWS < a.n_crows ? r0 + REDUCE_ROWS : a.n_crows;
+            const int total = (r1 - r0) * a.nvec;
+            for (int e = lane; e < total; e += 32) {
+                float4* y = Yv + (long long)__ldg(a.crows + r0 + e / a.nvec) * ldy_v + e % a.nvec;
+                *y = a.beta != 0.f ? vscale(a.beta, *y) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        __threadfence();
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) old = atomicAdd(c.ctrl + C_START_DONE, 1);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == nwarps - 1) {
+            __threadfence_system();
+            for (int i = lane; i < c.n_readers; i += 32) signal(c, F_READY, c.readers[i]);
+            for (int i = lane; i < c.n_contrib; i += 32) signal(c, F_READY, c.contrib[i]);
+        }
+    }
     if (c.phases & PH_MAIN) {
         if (!(c.phases & PH_START) && blockIdx.x == 0 && threadIdx.x == 0) stamp(c, T_START);
         bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
+        if (ATOMIC) ok = wait_all(c, F_READY, c.push_to, c.n_push, W_READY) && ok;
         const int n_pull = (a.n_recv_x + PULL_ROWS - 1) / PULL_ROWS;
         float4* Xv = reinterpret_cast<float4*>(a.X_loc);
         const long long ldx_v = a.ldx / 4;
@@ -512,9 +575,17 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
                 if (!ok) break;
             }
             const int i1 = i0 + SPMM_ITEMS_PER_TICKET < a.nitems ? i0 + SPMM_ITEMS_PER_TICKET : a.nitems;
-            for (int it = i0; it < i1; ++it)
-                spmm_warp_item<float, G, R, U>(__ldg(a.items + it), a.rowptr, a.colidx, a.val, Xv, ldx_v, a.nvec, emit,
-                                               a.lg, lane);
+            if constexpr (ATOMIC) {
+                const EmitOwnedOrAdd add{reinterpret_cast<float4*>(a.Y), a.ldy / 4, a.beta, a.n_owned_y, a.y_dst,
+                                         a.crow_flag, a.red_v4};
+                for (int it = i0; it < i1; ++it)
+                    spmm_warp_item<float, G, R, U>(__ldg(a.items + it), a.rowptr, a.colidx, a.val, Xv, ldx_v, a.nvec,
+                                                   add, a.lg, lane);
+            } else {
+                for (int it = i0; it < i1; ++it)
+                    spmm_warp_item<float, G, R, U>(__ldg(a.items + it), a.rowptr, a.colidx, a.val, Xv, ldx_v, a.nvec,
+                                                   emit, a.lg, lane);
+            }
         }
         main_epilogue(c, lane, nwarps);
     }
@@ -528,7 +599,7 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
         const float4* Sv = reinterpret_cast<const float4*>(a.slots) + (parity ? a.parity_off_v : 0);
         float4* Yv = reinterpret_cast<float4*>(a.Y);
         const long long lds_v = a.lds / 4, ldy_v = a.ldy / 4;
-        while (ok) {
+        while (ok && !ATOMIC) {  // atomic mode: the contributions are already in Y
             const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
             if (t >= n_chunks) break;
             const int r0 = t * REDUCE_ROWS;
@@ -583,9 +654,13 @@ SP3_API int sp3_fused_spmm_f32(const void* args, void* stream) {
     if (e != cudaSuccess) return (int)e;
     int G, R;
     pick_shape(a.nvec, &G, &R, true);
-#define SP3_FSPMM(GG, RR)                                                                        \
-    fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>                                                 \
-        <<<persistent_blocks(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>, 0), 256, 0, st>>>(a)
+#define SP3_FSPMM(GG, RR)                                                                               \
+    if (a.atomic)                                                                                       \
+        fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true>                                              \
+            <<<persistent_blocks(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true>, 0), 256, 0, st>>>(a);  \
+    else                                                                                                \
+        fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false>                                             \
+            <<<persistent_blocks(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false>, 0), 256, 0, st>>>(a)
     SP3_DISPATCH_GR(SP3_FSPMM)
 #undef SP3_FSPMM
     return (int)cudaGetLastError();

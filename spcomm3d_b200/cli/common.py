@@ -31,7 +31,7 @@ def base_parser(prog: str, description: str) -> argparse.ArgumentParser:
     ap.add_argument("--mesh", default=None, help="XxYxZ; default: balanced X>=Y for the given Z")
     ap.add_argument("--dtype", default=None, choices=["fp32", "fp64"])
     ap.add_argument("--variant", "--variants", dest="variant", default=None,
-                    help="comma list of sparse,sparseNRB,fused,dense")
+                    help="comma list of sparse,sparseNRB,fused,fused-atomic,dense")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--gen", default=None, help="synthetic matrix: uniform:M:N:deg | rmat:scale[:ef] | zipf:M:N[:a[:dmax]] | er:M:N:deg")
     ap.add_argument("--device", default=None, choices=["cpu", "cuda"])
@@ -76,7 +76,7 @@ class Runtime:
     def variants(self, args, default):
         v = args.variant.split(",") if args.variant else list(default)
         if self.device.type != "cuda" or self.dtype != torch.float32:
-            v = [x for x in v if x != "fused"]
+            v = [x for x in v if not x.startswith("fused")]
         return v
 
     def load_plan(self, args):

@@ -86,7 +86,7 @@ def main(argv=None):
                         recv_bytes += (plan.nnz - cs["POST"][1][1]) * es  # partial values from the fiber
                     gather_bytes = plan.nnz * op.k_loc * es  # dense rows fetched by the local kernel
                     vec = torch.tensor([ms, recv_bytes, recv_bytes, 0.0, 0.0], dtype=torch.float64, device=rt.device)
-                    if variant == "fused":
+                    if op.variant == "fused":
                         ph = op._fused.phase_ms()
                         vec[3], vec[4] = ph["pull"], ph["main"]
                     if rt.world > 1:
@@ -103,11 +103,11 @@ def main(argv=None):
                            "ms": round(ms_max, 4), "gflops": round(op.flops() / ms_max / 1e6, 1),
                            "comm_bytes_max_rank": float(mx[1]), "comm_bytes_total": float(sm[2]),
                            "roofline": {kk: (round(v, 4) if isinstance(v, float) else v) for kk, v in roof.items()}}
-                    if variant == "fused":
+                    if op.variant == "fused":
                         rec["pull_ms"] = round(float(mx[3]), 4)
                         rec["main_ms"] = round(float(mx[4]), 4)
                     rt.say(json.dumps(rec))
-                    if variant == "fused":
+                    if op.variant == "fused":
                         op._fused.check()
                     del op
     rt.finish()

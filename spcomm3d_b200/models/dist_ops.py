@@ -18,6 +18,9 @@ z-th slice of the k columns.  Variants:
                owners' memory over NVLink, computes, and pushes partial
                results to their owners (zero staging; the role of ref
                "sparseNB"); needs GPUs with peer access
+  "fused-atomic"  the fused kernels with the SpMM partial rows added into the
+               owners' result rows by atomics (no slot memory, no second pass,
+               sums not bitwise reproducible)
   "dense"      sparsity-agnostic: all-gather whole slabs, reduce-scatter
                (ref "dense", src/dcomm_setup.cpp)
 
@@ -128,6 +131,8 @@ class DistSDDMM(_Dist3DOp):
     kernel = "sddmm"
 
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
+        if variant == "fused-atomic":  # only SpMM has an atomic mode
+            variant = "fused"
         super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
         p = plan
         if variant == "fused":
@@ -207,11 +212,14 @@ class DistSpMM(_Dist3DOp):
     kernel = "spmm"
 
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
+        if variant == "fused-atomic":  # the fused kernel with partial rows added into the owners' rows by atomics
+            variant, kw = "fused", {**kw, "reduce": "atomic"}
         super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSpMM
-            self._fused = FusedSpMM(self, **{k_: v for k_, v in kw.items() if k_ in ("heap", "fabric", "timeout_s")})
+            self._fused = FusedSpMM(self, **{k_: v for k_, v in kw.items()
+                                             if k_ in ("heap", "fabric", "timeout_s", "reduce", "red_v4")})
             self.X_loc, self.Y_loc = self._fused.X_loc, self._fused.Y_loc
         else:
             self.X_loc, self.Y_loc = self._alloc_local(p.col), self._alloc_local(p.row)
@@ -220,6 +228,8 @@ class DistSpMM(_Dist3DOp):
         # into a buffer of their own
         if variant in ("sparse", "sparseNRB"):
             self.Y_owned = self.Y_loc[:p.row.n_owned]
+        elif variant == "fused" and self._fused.atomic:
+            self.Y_owned = self._fused.Y_heap   # peers add their partial rows into it
         else:
             self.Y_owned = torch.zeros(p.row.n_owned, self.k_loc, dtype=dtype, device=self.device)
         self.sched = None

@@ -59,7 +59,7 @@ class _SpmmArgs(C.Structure):
                 ("x_src", P), ("nvec", C.c_int), ("lg", _SpmmLong), ("n_owned_y", C.c_int), ("n_crows", C.c_int),
                 ("crows", P), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
                 ("ldy", C.c_longlong), ("beta", C.c_float), ("cptr", P), ("cslot", P), ("slots", P),
-                ("lds", C.c_longlong)]
+                ("lds", C.c_longlong), ("atomic", C.c_int), ("red_v4", C.c_int), ("crow_flag", P)]
 
 
 _checked_layout = False
@@ -110,7 +110,7 @@ class _FusedBase:
         if heap is None:
             if fabric is None:
                 fabric = IpcFabric(device=self.device)
-            heap = fabric.heap(self.region_sizes(self.plan, self.k_loc))
+            heap = fabric.heap(self.region_sizes_for(self.plan, self.k_loc))
         self.heap = heap
         self.rank = self.plan.rank
         self.epoch = 0
@@ -120,6 +120,9 @@ class _FusedBase:
         self.pad = heap.view("pad", torch.int32, (F_KINDS * MAX_RANKS,))
         self.peer_pad = self._dev_i64([heap.addr("pad", r) for r in range(heap.world)])
         self._keep = []
+
+    def region_sizes_for(self, plan, k_loc):
+        return self.region_sizes(plan, k_loc)
 
     def _dev_i64(self, values):
         return torch.from_numpy(np.asarray(values, dtype=np.int64).reshape(-1)).to(self.device)
@@ -299,16 +302,39 @@ class FusedSDDMM(_FusedBase):
 
 
 class FusedSpMM(_FusedBase):
+    """reduce="slots" (default): partial rows of rows owned elsewhere go to a slot at the owner, which adds
+    them in ascending source order (bitwise reproducible).  reduce="atomic": the result lives in the symmetric
+    heap (`Y_heap`) and partial rows are added into the owners' rows with atomics -- no slot memory, no second
+    pass, results depend on the order of the additions."""
+
     @staticmethod
-    def region_sizes(plan, k_loc: int) -> dict:
+    def region_sizes(plan, k_loc: int, reduce: str | None = None) -> dict:
         rb = k_loc * 4
+        if reduce is None:
+            reduce = os.environ.get("SP3_FUSED_SPMM_REDUCE", "slots")
+        if reduce == "atomic":
+            return {"pad": F_KINDS * MAX_RANKS * 4, "X": plan.col.n_local * rb, "slots": 0,
+                    "Y": _align(max(1, plan.row.n_owned) * rb)}
         return {"pad": F_KINDS * MAX_RANKS * 4, "X": plan.col.n_local * rb,
                 "slots": 2 * _align(plan.row.n_send * rb)}
 
-    def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0):
+    def region_sizes_for(self, plan, k_loc):
+        return self.region_sizes(plan, k_loc, self.reduce)
+
+    def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
+                 reduce: str | None = None, red_v4: bool | None = None):
+        if reduce is None:
+            reduce = os.environ.get("SP3_FUSED_SPMM_REDUCE", "slots")
+        if reduce not in ("slots", "atomic"):
+            raise ValueError(f"reduce must be 'slots' or 'atomic', got {reduce!r}")
+        self.reduce, self.atomic = reduce, reduce == "atomic"
+        if red_v4 is None:
+            red_v4 = os.environ.get("SP3_FUSED_RED_V4", "1") == "1"
         super().__init__(op, heap, fabric, timeout_s)
         p, h, k, rb = self.plan, self.heap, self.k_loc, self.row_bytes
         rp = p.row
+        if self.atomic and "Y" not in h.sizes:
+            raise ValueError("the heap was sized for reduce='slots'")
         self.X_loc = h.view("X", torch.float32, (p.col.n_local, k))
         # no local Y block: owned rows are written straight into the result, the others into their owners' slots
         self.Y_loc = None
@@ -321,8 +347,13 @@ class FusedSpMM(_FusedBase):
         roff = rp.recv_offsets()
         i_in_seg = np.arange(rp.n_recv, dtype=np.int64) - roff[rp.recv_peer]
         slot_row = rp.push_offset[rp.recv_peer] + i_in_seg
-        base = np.asarray(h.peer_base, dtype=np.int64) + h.offsets["slots"]
-        y_dst = base[np.asarray(row_r, dtype=np.int64)[rp.recv_peer]] + slot_row * rb
+        if self.atomic:
+            _, y_dst = self._side_tables(rp, "Y")   # address of every row I do not own inside its owner's Y
+            self.Y_heap = h.view("Y", torch.float32, (rp.n_owned, k))
+        else:
+            base = np.asarray(h.peer_base, dtype=np.int64) + h.offsets["slots"]
+            y_dst = base[np.asarray(row_r, dtype=np.int64)[rp.recv_peer]] + slot_row * rb
+            self.Y_heap = None
         self.y_dst = self._dev_i64(y_dst if y_dst.size else [0])
         # contributions to my owned rows: slot rows grouped by owned row, ascending source
         order = np.argsort(rp.send_idx, kind="stable")
@@ -336,6 +367,9 @@ class FusedSpMM(_FusedBase):
         self.sched = cuda_ops.SpmmSchedule(op.rowptr)
         carry, ldc = self.sched.carry_for(k, torch.float32, self.device)
         self.slots = h.view("slots", torch.float32, (h.sizes["slots"] // 4,))
+        flag = np.zeros(max(1, rp.n_owned), np.uint8)
+        flag[crows] = 1
+        self.crow_flag = torch.from_numpy(flag).to(self.device)
         a = self.args = _SpmmArgs()
         read_from = [col_r[q] for q in range(p.col.npeers) if p.col.recv_counts[q] > 0]
         readers = [col_r[q] for q in range(p.col.npeers) if p.col.send_counts[q] > 0]
@@ -359,11 +393,16 @@ class FusedSpMM(_FusedBase):
         a.parity_off_v = half // 16
         a.cptr, a.cslot = self.cptr.data_ptr(), self.cslot.data_ptr()
         a.slots, a.lds = self.slots.data_ptr(), k
+        a.atomic, a.red_v4, a.crow_flag = int(self.atomic), int(bool(red_v4)), self.crow_flag.data_ptr()
+        if self.atomic:
+            a.parity_off_v = 0
 
     def launch(self, Y: torch.Tensor, beta: float, phases=PH_ALL, new_epoch=True):
         if new_epoch:
             self.epoch += 1
         a = self.args
+        if self.atomic and Y.data_ptr() != self.Y_heap.data_ptr():
+            raise ValueError("reduce='atomic': the result must be this op's Y_heap (peers add into it)")
         a.Y, a.ldy, a.beta = Y.data_ptr(), Y.stride(0) if Y.shape[0] > 1 else self.k_loc, float(beta)
         self._launch(native.cuda().sp3_fused_spmm_f32, phases)
 

@@ -27,7 +27,10 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
     _, plan = build_my_plan(m, mesh, rank, seed=3)
     fabric = IpcFabric(device=dev)
     for variant in variants:
-        kw = {"fabric": fabric, "timeout_s": 10.0} if variant == "fused" else {}
+        # "fused-atomic": the fused kernels with partial SpMM rows added into the owners' rows by atomics
+        reduce = "atomic" if variant == "fused-atomic" else "slots"
+        variant = "fused" if variant == "fused-atomic" else variant
+        kw = {"fabric": fabric, "timeout_s": 10.0, "reduce": reduce} if variant == "fused" else {}
         sd = DistSDDMM(plan, groups, k, torch.float32, dev, variant, **kw)
         sp = DistSpMM(plan, groups, k, torch.float32, dev, variant, **kw)
         for epoch in range(2):
@@ -81,5 +84,4 @@ def test_all_variants_on_real_peers():
     n = torch.cuda.device_count()
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     for meshstr in _meshes(n):
-        run_ranks(_rank_main, n, meshstr, "zipf:3000:4000:1.6:700", 64, ["fused", "sparseNRB", "sparse", "dense"],
-                  backend="nccl")
+        run_ranks(_rank_main, n, meshstr, "zipf:3000:4000:1.6:700", 64, ["fused", "fused-atomic", "sparseNRB", "sparse", "dense"], backend="nccl")
