@@ -47,7 +47,7 @@ USE_TMA = os.environ.get("SP3_SDDMM_TMA", "0") == "1"
 
 def sddmm_tma(rowidx, colidx, svals, A, B, out, status=None):
     """SDDMM whose B rows are staged in shared memory by TMA `tile::gather4`
-    copies (csrc/kernels/tma_ops.cu).  fp32, k a multiple of 4 in [8, 256]."""
+    copies (csrc/kernels/tma_ops.cu).  fp32, k a multiple of 8 in [8, 256]."""
     if A.dtype != torch.float32:
         raise TypeError("the TMA kernel is fp32")
     st = new_status(A.device) if status is None else status
@@ -61,7 +61,7 @@ def sddmm_tma(rowidx, colidx, svals, A, B, out, status=None):
 
 
 def sddmm(rowidx, colidx, svals, A, B, out):
-    if USE_TMA and A.dtype == torch.float32 and A.shape[1] % 4 == 0 and 8 <= A.shape[1] <= 256:
+    if USE_TMA and A.dtype == torch.float32 and A.shape[1] % 8 == 0 and 8 <= A.shape[1] <= 256:
         return sddmm_tma(rowidx, colidx, svals, A, B, out)
     fn = getattr(native.cuda(), f"sp3_cuda_sddmm_{_F[A.dtype]}")
     _ck(fn(rowidx.shape[0], native.ptr(rowidx), native.ptr(colidx), native.ptr(svals), native.ptr(A), _ld(A),
@@ -136,7 +136,29 @@ class SpmmSchedule:
         return self.carry, self.carry.stride(0)
 
 
+USE_SPMM_TMA = os.environ.get("SP3_SPMM_TMA", "0") == "1"
+
+
+def spmm_tma(rowidx, colidx, vals, X, Y, beta=0.0, status=None):
+    """SpMM whose X rows are staged in shared memory by TMA `tile::gather4`
+    copies (csrc/kernels/tma_ops.cu).  rowidx ascending (CSR order), fp32, k a
+    multiple of 8 in [8, 256].  Rows that span several 256-nonzero units are
+    summed with atomics (not bitwise reproducible)."""
+    if X.dtype != torch.float32:
+        raise TypeError("the TMA kernel is fp32")
+    st = new_status(X.device) if status is None else status
+    rc = native.cuda().sp3_cuda_spmm_tma_f32(rowidx.shape[0], native.ptr(rowidx), native.ptr(colidx), native.ptr(vals),
+                                             native.ptr(X), _ld(X), X.shape[0], X.shape[1], float(beta),
+                                             native.ptr(Y), _ld(Y), Y.shape[0], native.ptr(st), _stream())
+    if rc < 0:
+        raise ValueError({-1: "shape not supported by the TMA kernel", -2: "tensor map encoding failed"}[rc])
+    _ck(rc, "spmm_tma", 2)
+    return Y
+
+
 def spmm(rowptr, rowidx, colidx, vals, X, Y, beta, sched: SpmmSchedule | None):
+    if USE_SPMM_TMA and X.dtype == torch.float32 and X.shape[1] % 8 == 0 and 8 <= X.shape[1] <= 256:
+        return spmm_tma(rowidx, colidx, vals, X, Y, beta)
     if sched is None:
         sched = SpmmSchedule(rowptr)
     carry, ldc = sched.carry_for(X.shape[1], X.dtype, X.device)

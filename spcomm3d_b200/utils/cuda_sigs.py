@@ -20,6 +20,7 @@ CUDA_SIGS = {
     "sp3_cuda_invert_perm": ("int", "i64 p p p p"),
     "sp3_cuda_touch_masks": ("int", "i64 p p p p p p p"),
     "sp3_cuda_sddmm_tma_f32": ("int", "i64 p p p p i64 p i64 i64 int p p p"),
+    "sp3_cuda_spmm_tma_f32": ("int", "i64 p p p p i64 i64 int f32 p i64 i64 p p"),
     "sp3_cuda_sddmm_orig_f32": ("int", "i64 p p p p i64 p i64 int p p p"),
     "sp3_cuda_sddmm_panel_f32": ("int", "int p p p p p p p p i64 int p i64 int p p p"),
     "sp3_cuda_spmm_panel_f32": ("int", "int p p p p p p p p p i64 int p i64 int p p"),

@@ -182,6 +182,27 @@ def test_sddmm_tma_gather(k):
     assert (out.cpu().double() - ref).abs().max() <= 2e-5 * ref.abs().max() * k ** 0.5
 
 
+@pytest.mark.parametrize("k", [8, 32, 64, 128, 256, 24])
+def test_spmm_tma_gather(k):
+    """X rows staged by TMA tile::gather4 copies; rows with zero, few and thousands of nonzeros; beta."""
+    from spcomm3d_b200.ops import cuda_ops
+    nrows, ncols = 3000, 2500
+    rowptr, rowidx, colidx, vals = _csr(nrows, ncols, _degs(nrows, 1), 2)
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(ncols, k, generator=g, dtype=torch.float64)
+    Y0 = torch.randn(nrows, k, generator=g, dtype=torch.float64)
+    S = torch.sparse_coo_tensor(torch.stack([rowidx.long(), colidx.long()]), vals, (nrows, ncols)).coalesce()
+    prod = torch.sparse.mm(S, X)
+    st = cuda_ops.new_status("cuda")
+    for beta in (0.0, 0.5):
+        Y = Y0.float().cuda() if beta else torch.full((nrows, k), float("nan"), dtype=torch.float32, device="cuda")
+        cuda_ops.spmm_tma(rowidx.cuda(), colidx.cuda(), vals.float().cuda(), X.float().cuda(), Y, beta, st)
+        torch.cuda.synchronize()
+        assert st.tolist()[0] == 0, st.tolist()
+        ref = prod + beta * Y0
+        assert (Y.cpu().double() - ref).abs().max() <= 2e-5 * ref.abs().max() * 8
+
+
 @pytest.mark.parametrize("k", [32, 64, 128])
 def test_sddmm_dense_panels_on_tensor_cores(k):
     """Hub block x hub columns goes through tcgen05 TF32 tiles, the rest through the gather kernel."""
