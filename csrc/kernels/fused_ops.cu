@@ -241,6 +241,7 @@ struct FusedSddmmArgs {
                                   // 0: they are staged in `part` and pushed in bulk once all are there;
                                   // 2: staged, and every warp pushes the range of a ticket right after computing
                                   //    it (needs orig == null: a ticket's values are then one contiguous range)
+                                  // 3: staged in a multicast-bound buffer, nothing pushed, reduced in the switch
     // Overlap of pulls and compute: the kernel walks the nonzeros in the order "those whose B row is owned
     // first, then those that need a pulled row" (rowidx / colidx / sval are given in that order);
     // orig[i] is the position of nonzero i in the plan's value order (null: identity), nnz_free the
@@ -253,7 +254,26 @@ struct FusedSddmmArgs {
     int n_recv_a;
     const float4* const* a_src;
     float* A_stage;
+    // Z reduction inside the NVSwitch (direct_push == 3): `part` is this rank's buffer of a symmetric allocation
+    // that is bound to a multicast object over the Z fiber ([2][part_stride] values, one half per epoch parity);
+    // nothing is pushed, and in FINISH the owner of a slice reads mc_part (the multicast address of the same
+    // allocation) with `multimem.ld_reduce.add`, which returns the sum over all fiber ranks.
+    const float* mc_part;
+    long long part_stride;
 };
+
+// Sum over all devices of a multicast object, added in the NVSwitch (NVLS); `p` is a multicast address.
+__device__ __forceinline__ float multimem_add_f32(const float* p) {
+    float v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 multimem_add_v4(const float* p) {
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
 
 // Where a value goes.  Z == 1: into the result.  Z > 1, staged mode: into the local array `part` at its
 // position in the plan's value order; the slices of the other fiber ranks are then pushed in bulk by the
@@ -307,7 +327,9 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull};
         const int direct = a.Z > 1 && a.direct_push == 1;
         const bool self_push = a.Z > 1 && a.direct_push == 2 && a.orig == nullptr;
-        const StorePartial store{a.sval, a.orig, a.Z > 1 ? a.part : a.out, a.zbuf, direct, a.Z, a.my_z, parity,
+        const bool in_switch = a.Z > 1 && a.direct_push == 3;
+        float* const part = in_switch ? a.part + (long long)parity * a.part_stride : a.part;
+        const StorePartial store{a.sval, a.orig, a.Z > 1 ? part : a.out, a.zbuf, direct, a.Z, a.my_z, parity,
                                  a.zbase, a.zrem, a.zwidth};
         float4* Bv = reinterpret_cast<float4*>(a.B_loc);
         const long long ldb_v = a.ldb / 4;
@@ -374,7 +396,7 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
             }
         }
         while (ok && pulls_left) pulls_left = pull_one();  // no compute left but tiles remain (tiny blocks)
-        if (a.Z > 1 && !direct && !self_push) {
+        if (a.Z > 1 && !direct && !self_push && !in_switch) {
             // all partial values of this rank are in `part` once every warp has passed this point; then the
             // slices of the other fiber ranks travel as contiguous, fully coalesced remote stores
             __threadfence();
@@ -412,7 +434,29 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
             const int n_chunks = (int)((my_len + REDUCE_ELEMS - 1) / REDUCE_ELEMS);
             const float* mine = a.zbuf[a.my_z] + (long long)parity * a.Z * a.zwidth;
             const float* own = a.part + slice_off(a.my_z, a.zbase, a.zrem);
-            while (ok) {
+            while (ok && a.direct_push == 3) {
+                // one load per 16 bytes returns the sum over the fiber, added inside the switch; positions of
+                // the multicast buffer that are not 16-byte aligned (slice edges) are read one value at a time
+                const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
+                if (t >= n_chunks) break;
+                const long long s0 = slice_off(a.my_z, a.zbase, a.zrem);
+                const float* src = a.mc_part + (long long)parity * a.part_stride;   // 16-byte aligned
+                const long long j0 = s0 + (long long)t * REDUCE_ELEMS;
+                const long long j1 = j0 + REDUCE_ELEMS < s0 + my_len ? j0 + REDUCE_ELEMS : s0 + my_len;
+                const long long b0 = (j0 + 3) & ~3ll, b1 = j1 & ~3ll;     // aligned body [b0, b1)
+                if (b0 >= b1) {
+                    for (long long j = j0 + lane; j < j1; j += 32) a.out[j - s0] = multimem_add_f32(src + j);
+                } else {
+                    for (long long j = j0 + lane; j < b0; j += 32) a.out[j - s0] = multimem_add_f32(src + j);
+                    for (long long j = b0 + 4 * lane; j < b1; j += 128) {
+                        const float4 v = multimem_add_v4(src + j);
+                        float* o = a.out + (j - s0);
+                        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+                    }
+                    for (long long j = b1 + lane; j < j1; j += 32) a.out[j - s0] = multimem_add_f32(src + j);
+                }
+            }
+            while (ok && a.direct_push != 3) {
                 const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
                 if (t >= n_chunks) break;
                 const long long e0 = (long long)t * REDUCE_ELEMS;

@@ -31,7 +31,7 @@ def base_parser(prog: str, description: str) -> argparse.ArgumentParser:
     ap.add_argument("--mesh", default=None, help="XxYxZ; default: balanced X>=Y for the given Z")
     ap.add_argument("--dtype", default=None, choices=["fp32", "fp64"])
     ap.add_argument("--variant", "--variants", dest="variant", default=None,
-                    help="comma list of sparse,sparseNRB,fused,fused-atomic,dense")
+                    help="comma list of sparse,sparseNRB,fused,fused-atomic,fused-multimem,dense")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--gen", default=None, help="synthetic matrix: uniform:M:N:deg | rmat:scale[:ef] | zipf:M:N[:a[:dmax]] | er:M:N:deg")
     ap.add_argument("--device", default=None, choices=["cpu", "cuda"])

@@ -109,6 +109,9 @@ def main(argv=None):
                     rt.say(json.dumps(rec))
                     if op.variant == "fused":
                         op._fused.check()
+                        if hasattr(op._fused, "release"):  # multicast binding: dropped by all ranks together
+                            rt.barrier()
+                            op._fused.release()
                     del op
     rt.finish()
 

@@ -21,6 +21,9 @@ z-th slice of the k columns.  Variants:
   "fused-atomic"  the fused kernels with the SpMM partial rows added into the
                owners' result rows by atomics (no slot memory, no second pass,
                sums not bitwise reproducible)
+  "fused-multimem"  the fused kernels with the SDDMM Z reduction done inside the
+               NVSwitch: partial values stay in a multicast-bound buffer and the
+               slice owners read them with `multimem.ld_reduce.add` (NVLS)
   "dense"      sparsity-agnostic: all-gather whole slabs, reduce-scatter
                (ref "dense", src/dcomm_setup.cpp)
 
@@ -133,12 +136,14 @@ class DistSDDMM(_Dist3DOp):
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
         if variant == "fused-atomic":  # only SpMM has an atomic mode
             variant = "fused"
+        if variant == "fused-multimem":  # Z reduction of the partial values inside the NVSwitch
+            variant, kw = "fused", {**kw, "zreduce": "multimem"}
         super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSDDMM
             self._fused = FusedSDDMM(self, **{k_: v for k_, v in kw.items() if k_ in (
-                "heap", "fabric", "timeout_s", "overlap", "direct_push", "stage_a")})
+                "heap", "fabric", "timeout_s", "overlap", "direct_push", "stage_a", "zreduce")})
             self.A_loc, self.B_loc = self._fused.A_loc, self._fused.B_loc
         else:
             self.A_loc, self.B_loc = self._alloc_local(p.row), self._alloc_local(p.col)
@@ -214,6 +219,8 @@ class DistSpMM(_Dist3DOp):
     def __init__(self, plan, groups, k, dtype=torch.float32, device="cpu", variant="sparseNRB", **kw):
         if variant == "fused-atomic":  # the fused kernel with partial rows added into the owners' rows by atomics
             variant, kw = "fused", {**kw, "reduce": "atomic"}
+        if variant == "fused-multimem":  # only SDDMM has a Z reduction
+            variant = "fused"
         super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
         p = plan
         if variant == "fused":

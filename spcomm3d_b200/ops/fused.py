@@ -45,7 +45,7 @@ class _SddmmArgs(C.Structure):
                 ("n_recv_b", C.c_int), ("b_src", P), ("nvec", C.c_int), ("Z", C.c_int), ("my_z", C.c_int),
                 ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P),
                 ("part", P), ("direct_push", C.c_int), ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int),
-                ("n_recv_a", C.c_int), ("a_src", P), ("A_stage", P)]
+                ("n_recv_a", C.c_int), ("a_src", P), ("A_stage", P), ("mc_part", P), ("part_stride", C.c_longlong)]
 
 
 class _SpmmLong(C.Structure):
@@ -201,8 +201,14 @@ class FusedSDDMM(_FusedBase):
                 "zbuf": 2 * Z * zwidth * 4 if Z > 1 else 0}
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
-                 overlap: bool = True, direct_push: bool | None = None, stage_a: bool | None = None):
+                 overlap: bool = True, direct_push: bool | None = None, stage_a: bool | None = None,
+                 zreduce: str | None = None):
         super().__init__(op, heap, fabric, timeout_s)
+        if zreduce is None:
+            zreduce = os.environ.get("SP3_FUSED_ZREDUCE", "push")
+        if zreduce not in ("push", "multimem"):
+            raise ValueError(f"zreduce must be 'push' or 'multimem', got {zreduce!r}")
+        self.zreduce = zreduce
         p, h, k = self.plan, self.heap, self.k_loc
         Z, z = p.mesh.Z, p.coords[2]
         # A block: my owned rows (peers read them in place) followed by room for staged copies of the remote
@@ -276,7 +282,12 @@ class FusedSDDMM(_FusedBase):
         a.zwidth = self.zwidth
         a.zbuf = self.zbuf_ptrs.data_ptr()
         a.out = self.out.data_ptr()
-        self.part = torch.zeros(p.nnz if Z > 1 else 1, dtype=torch.float32, device=self.device)
+        self._mc = None
+        if Z > 1 and self.zreduce == "multimem":
+            self.part, a.mc_part, a.part_stride = self._multicast_part(op, p.nnz)
+        else:
+            self.part = torch.zeros(p.nnz if Z > 1 else 1, dtype=torch.float32, device=self.device)
+            a.mc_part, a.part_stride = None, 0
         a.part = self.part.data_ptr()
         # Push mode of the partial values (Z > 1).  1: remote stores as the values are computed -- a lane group
         # stores (k_loc/8) consecutive values at a time, which only pays for >= 32 bytes; 0: staged in `part`,
@@ -289,7 +300,33 @@ class FusedSDDMM(_FusedBase):
         direct_push = int(direct_push)
         if direct_push == 2 and a.orig:
             direct_push = 0
+        if Z > 1 and self.zreduce == "multimem":
+            direct_push = 3   # nothing is pushed: the slice owners reduce through the multicast address
         a.direct_push = self.push_mode = direct_push
+
+    def _multicast_part(self, op, nnz: int):
+        """Partial-value buffer [2][nnz rounded up to 4] in torch symmetric memory, bound to a multicast object
+        over the Z fiber (NVLS).  Returns (local tensor, multicast address, values per half)."""
+        group = getattr(op, "_fiber_group", None)
+        if group is None:
+            raise ValueError("zreduce='multimem' needs the fiber process group (real ranks, not emulation)")
+        import torch.distributed._symmetric_memory as symm_mem
+        stride = (nnz + 3) // 4 * 4
+        t = symm_mem.empty(2 * max(stride, 4), dtype=torch.float32, device=self.device)
+        hdl = symm_mem.rendezvous(t, group=group)
+        mc = int(hdl.multicast_ptr)
+        if mc == 0:
+            raise ValueError("zreduce='multimem': this system gives no multicast (NVLS) address")
+        t.zero_()
+        self._mc = hdl
+        return t, mc, stride
+
+    def release(self):
+        """Drops the multicast binding (collective over the fiber when zreduce='multimem'): call it on every
+        rank, with no kernel in flight, before a rank exits."""
+        if self._mc is not None:
+            torch.cuda.synchronize(self.device)
+            self._mc, self.part = None, None
 
     def launch(self, phases=PH_ALL, new_epoch=True):
         if new_epoch:

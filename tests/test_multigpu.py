@@ -56,6 +56,41 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
             if yref.numel():
                 err = (y.cpu().double() - yref).abs().max()
                 assert err <= 2e-5 * max(1.0, yref.abs().max()) * 8, (variant, "spmm", float(err))
+    # Z reduction inside the NVSwitch (multimem.ld_reduce over a multicast-bound buffer of the fiber).  No rank
+    # raises while the buffer is bound: errors are collected, agreed on, and reported after the release.
+    if mesh.Z > 1:
+        import torch.distributed as dist
+        bad = torch.zeros(1, device=dev)
+        sd = None
+        try:
+            sd = DistSDDMM(plan, groups, k, torch.float32, dev, "fused-multimem", fabric=fabric, timeout_s=10.0)
+        except ValueError as e:  # no multicast support on this system: the same answer on every rank
+            print(f"rank {rank}: multimem variant not available: {e}")
+        if sd is not None:
+            for epoch in range(3):
+                A = generate.fill_rows(np.arange(m.nrows), k, 0, k, seed=7 + epoch, stream=1, dtype=np.float64)
+                B = generate.fill_rows(np.arange(m.ncols), k, 0, k, seed=7 + epoch, stream=2, dtype=np.float64)
+                sd.fill_owned(sd.A_owned, plan.row.owned_gids, seed=7 + epoch, stream=1)
+                sd.fill_owned(sd.B_owned, plan.col.owned_gids, seed=7 + epoch, stream=2)
+                sd.poison_unowned()
+                c = sd.run_async()   # no status check here: nothing may raise while the buffer is bound
+                off, ln = plan.owned_nnz_slice()
+                mine = CooMatrix(m.nrows, m.ncols, plan.global_rows()[off:off + ln], plan.global_cols()[off:off + ln],
+                                 plan.vals[off:off + ln])
+                ref = oracle.sddmm_ref(mine, A, B)
+                if c.shape[0] != ln or (ln and not bool(
+                        (c.cpu().double() - ref).abs().max() <= 2e-5 * max(1.0, ref.abs().max()) * k ** 0.5)):
+                    bad += 1
+            status = sd._fused.status.tolist()
+            if status[0] != 0:
+                bad += 100
+            torch.cuda.synchronize(dev)
+            dist.barrier()
+            sd._fused.release()
+            del sd
+            dist.barrier()
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        assert float(bad) == 0, ("fused-multimem", float(bad))
     # attention-style chain on the fused kernels: Y = (S o (A B^T)) X with X = B
     from spcomm3d_b200.models.layer import GatLayer
     layer = GatLayer(plan, groups, k, torch.float32, dev, "fused", fabric=fabric, timeout_s=10.0)
