@@ -120,9 +120,19 @@ def _build(lib: Path, srcs, hdrs, cmd, force=False, verbose=False) -> bool:
     return True
 
 
+def host_sanitized() -> bool:
+    """SP3_HOST_SANITIZE=1 selects a build of the host library with AddressSanitizer and
+    UndefinedBehaviorSanitizer (libsp3host_san.so).  The process must have the ASan runtime loaded first
+    (LD_PRELOAD of `gcc -print-file-name=libasan.so`); tests/test_host_sanitizers.py runs such a child."""
+    return os.environ.get("SP3_HOST_SANITIZE", "0") == "1"
+
+
 def host_build_cmd():
-    return ["g++", "-std=c++17", "-O3", "-fopenmp", "-fPIC", "-shared", "-fvisibility=hidden",
-            f"-I{CSRC / 'host'}"]
+    cmd = ["g++", "-std=c++17", "-fopenmp", "-fPIC", "-shared", "-fvisibility=hidden", f"-I{CSRC / 'host'}"]
+    if host_sanitized():
+        return cmd + ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+                      "-fno-sanitize-recover=undefined"]
+    return cmd + ["-O3"]
 
 
 def cuda_build_cmd(verbose_ptxas=False):
@@ -136,7 +146,7 @@ def cuda_build_cmd(verbose_ptxas=False):
 
 
 def build_host(force=False, verbose=False) -> Path:
-    lib = LIBDIR / "libsp3host.so"
+    lib = LIBDIR / ("libsp3host_san.so" if host_sanitized() else "libsp3host.so")
     _build(lib, _sources("host", {".cpp"}), _sources("host", {".hpp"}), host_build_cmd(), force, verbose)
     return lib
 
