@@ -6,8 +6,9 @@ gloo on CPUs).  It plays the role of the reference's SparseComm<T>
 (src/comm.hpp:28-199): `expand` = pack + P2P + unpack (copy_to_sendbuff :90,
 issue_Irecvs/Sends/Waitall :105-139, copy_from_recvbuff :166), `reduce` = the
 role-swapped handle of SpMM's post step with the owner-side sum
-(SUM_from_recvbuff :178-189, src/comm_setup.cpp:778-784).  One
-`all_to_all_single` with per-peer split sizes replaces the Irecv/Send loop.
+(SUM_from_recvbuff :178-189, src/comm_setup.cpp:778-784).  Transport: one
+`all_to_all_single` with per-peer split sizes, or batched isend/irecv to the
+actual neighbours only (`transport="p2p"`).
 
 Staging modes (the reference's three SDDMM instances,
 src/distributed_comp.cpp:141-284):
@@ -25,6 +26,8 @@ another.
 These engines are the measured baseline of the framework, not its product.
 """
 from __future__ import annotations
+
+import os
 
 import time
 
@@ -89,10 +92,21 @@ def _splits(counts, unit=1):
 
 
 class SparseExchange:
-    def __init__(self, side: SidePlan, group, k_loc: int, dtype, device, mode: str = "nrb", timer=None):
+    """Sparsity-aware exchange of dense rows along one mesh line with library collectives.
+
+    mode: "buffered" (send and receive staging) or "nrb" (rows land in place).
+    transport: "alltoall" -- one `all_to_all_single` with per-peer splits (the role of the reference's
+    MPI_Neighbor_alltoallv path, src/comm.hpp:149-156); "p2p" -- one receive and one send per actual neighbour,
+    batched (the reference's Irecv / Send / Waitall path, src/comm.hpp:105-139).  Default from SP3_TRANSPORT."""
+
+    def __init__(self, side: SidePlan, group, k_loc: int, dtype, device, mode: str = "nrb", timer=None,
+                 transport: str | None = None):
         if mode not in ("buffered", "nrb"):
             raise ValueError("mode must be 'buffered' or 'nrb'")
-        self.side, self.group, self.k, self.mode = side, group, k_loc, mode
+        transport = transport or os.environ.get("SP3_TRANSPORT", "alltoall")
+        if transport not in ("alltoall", "p2p"):
+            raise ValueError("transport must be 'alltoall' or 'p2p'")
+        self.side, self.group, self.k, self.mode, self.transport = side, group, k_loc, mode, transport
         self.device, self.dtype = torch.device(device), dtype
         self.timer = timer
         self.send_idx = torch.from_numpy(side.send_idx).to(self.device)
@@ -108,6 +122,24 @@ class SparseExchange:
 
     def _span(self, name):
         return self.timer.span(name) if self.timer is not None else _NullSpan()
+
+    def _exchange(self, recv: torch.Tensor, send: torch.Tensor, recv_split, send_split):
+        """Rows send[...] to the peers, rows from the peers into recv[...] (both grouped by peer, ascending)."""
+        if self.transport == "alltoall":
+            dist.all_to_all_single(recv, send, recv_split, send_split, group=self.group)
+            return
+        ops, ro, so = [], 0, 0
+        for p in range(self.side.npeers):
+            rc, sc = recv_split[p], send_split[p]
+            if p != self.side.me:
+                if rc:
+                    ops.append(dist.P2POp(dist.irecv, recv[ro:ro + rc], group=self.group, group_peer=p))
+                if sc:
+                    ops.append(dist.P2POp(dist.isend, send[so:so + sc], group=self.group, group_peer=p))
+            ro, so = ro + rc, so + sc
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
 
     # statistics in the reference's units: messages = neighbour counts, volume
     # = elements (rows x k_loc), src/comm_stats.cpp:62-65
@@ -126,7 +158,7 @@ class SparseExchange:
         with self._span("commcpy"):
             local.gather_rows(self.send_idx, buf[:s.n_owned], self.send_buf)
         target = self.recv_buf if self.mode == "buffered" else buf[s.n_owned:]
-        dist.all_to_all_single(target, self.send_buf, self.recv_split, self.send_split, group=self.group)
+        self._exchange(target, self.send_buf, self.recv_split, self.send_split)
         if self.mode == "buffered":
             with self._span("commcpy"):
                 local.scatter_rows(self.recv_pos, self.recv_buf, buf)
@@ -139,8 +171,7 @@ class SparseExchange:
         s = self.side
         if self.trivial:
             return buf
-        dist.all_to_all_single(self.send_buf, buf[s.n_owned:].contiguous(), self.send_split, self.recv_split,
-                               group=self.group)
+        self._exchange(self.send_buf, buf[s.n_owned:].contiguous(), self.send_split, self.recv_split)
         with self._span("commcpy"):
             owned = buf[:s.n_owned]
             for p in range(s.npeers):

@@ -66,6 +66,13 @@ def test_2x2x2_all_variants():
     run_ranks(_check_many, 8, "2x2x2", cases, K, None)
 
 
+def test_p2p_transport(monkeypatch):
+    """One receive and one send per actual neighbour instead of the all-to-all with split sizes."""
+    monkeypatch.setenv("SP3_TRANSPORT", "p2p")   # inherited by the spawned ranks
+    cases = [(kern, var) for kern in ("sddmm", "spmm") for var in ("sparse", "sparseNRB")]
+    run_ranks(_check_many, 6, "3x2x1", cases, 12, None)
+
+
 @pytest.mark.parametrize("meshstr,k", [("4x2x1", 32), ("1x1x8", 20), ("2x1x2", 7), ("1x3x1", 16), ("3x1x1", 16)])
 def test_other_meshes(meshstr, k):
     from spcomm3d_b200.parallel.mesh import Mesh3D
