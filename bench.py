@@ -39,7 +39,8 @@ def parse_args():
     ap.add_argument("--gen", default="rmat:22:16", help="matrix spec (utils.generate.from_spec)")
     ap.add_argument("--k", type=int, default=128)
     ap.add_argument("--mesh", default=None, help="XxYxZ (default: the fastest measured mesh for N = 2, 4, 8)")
-    ap.add_argument("--variant", default=None, choices=[None, "fused", "sparse", "sparseNRB", "dense"])
+    ap.add_argument("--variant", default=None,
+                    choices=[None, "fused", "fused-atomic", "fused-multimem", "sparse", "sparseNRB", "dense"])
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--panels", action="store_true",
