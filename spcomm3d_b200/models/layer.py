@@ -72,14 +72,32 @@ class SddmmSpmmStep:
 
     def run_e2e(self):
         """Copies the step's inputs A and B from pinned host memory (X of the
-        SpMM is B: one device-to-device copy), runs SDDMM then SpMM and reads
-        back the checksums of this rank's results (two fp64 scalars)."""
+        SpMM is B: one device-to-device copy), runs SDDMM and SpMM (the SpMM
+        overlaps the copy of A) and reads back the checksums of this rank's
+        results (two fp64 scalars)."""
         sd, sp, h = self.sddmm, self.spmm, self.host
-        sd.A_owned.copy_(h["A"], non_blocking=True)
-        sd.B_owned.copy_(h["B"], non_blocking=True)
-        sp.X_owned.copy_(sd.B_owned)
-        c = sd.run_async()
-        y = sp.run_async()
+        if self.device.type == "cuda":
+            # B first; while A follows on a copy stream the SpMM (which needs only X = B) already runs
+            main = torch.cuda.current_stream(self.device)
+            if getattr(self, "_copy_stream", None) is None:
+                self._copy_stream = torch.cuda.Stream(self.device)
+                self._ev_b, self._ev_a = torch.cuda.Event(), torch.cuda.Event()
+            sd.B_owned.copy_(h["B"], non_blocking=True)
+            self._ev_b.record(main)
+            self._copy_stream.wait_event(self._ev_b)   # also orders this copy of A after the previous step's SDDMM
+            with torch.cuda.stream(self._copy_stream):
+                sd.A_owned.copy_(h["A"], non_blocking=True)
+                self._ev_a.record(self._copy_stream)
+            sp.X_owned.copy_(sd.B_owned)
+            y = sp.run_async()
+            main.wait_event(self._ev_a)
+            c = sd.run_async()
+        else:
+            sd.A_owned.copy_(h["A"], non_blocking=True)
+            sd.B_owned.copy_(h["B"], non_blocking=True)
+            sp.X_owned.copy_(sd.B_owned)
+            c = sd.run_async()
+            y = sp.run_async()
         if self.device.type == "cuda":
             from ..ops import cuda_ops
             self._sums[0:1].copy_(cuda_ops.checksum(c))
