@@ -123,6 +123,11 @@ class ClockSampler:
 
 
 def run_ours(args):
+    # torchrun pins OMP_NUM_THREADS to 1; matrix generation and plan building (host library, OpenMP) are setup
+    # work outside the timed region and may use this rank's share of the cores
+    world_env = int(os.environ.get("WORLD_SIZE", 1))
+    if os.environ.get("OMP_NUM_THREADS") == "1" and world_env > 1:
+        os.environ["OMP_NUM_THREADS"] = str(max(1, min(16, (os.cpu_count() or 1) // world_env)))
     import torch
     import torch.distributed as dist
     from spcomm3d_b200.models.layer import SddmmSpmmStep
