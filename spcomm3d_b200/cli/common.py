@@ -15,7 +15,7 @@ import sys
 import torch
 
 from ..parallel.mesh import Mesh3D, MeshGroups, dims_create
-from ..parallel.partition import Directory, distribute_from_file
+from ..parallel.partition import distribute_from_file
 from ..parallel.plan import build_my_plan, build_rank_plan
 from ..utils import binfmt, generate
 

@@ -13,7 +13,6 @@ from __future__ import annotations
 
 import sys
 
-import torch
 
 from ..models.dist_ops import DistSDDMM, DistSpMM
 from ..utils import generate

@@ -18,7 +18,7 @@ import os
 import numpy as np
 import torch
 
-from ..parallel.symm import ALIGN, IpcFabric, SymmHeap, _align
+from ..parallel.symm import IpcFabric, SymmHeap, _align
 from ..utils import native
 from . import cuda_ops
 

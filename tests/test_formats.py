@@ -1,5 +1,4 @@
 """conv2bin binary format, MatrixMarket quirks, native conv2bin tool."""
-import os
 import struct
 import subprocess
 

@@ -3,7 +3,6 @@ nonzero lands in exactly one place, panel entries agree with the panel tables,
 groups respect row blocks and the cap on groups per block."""
 import numpy as np
 import pytest
-import torch
 
 from spcomm3d_b200.ops.panel import PANEL_M, PANEL_N, PanelSpMM
 
