@@ -48,5 +48,31 @@ def build(verbose=False) -> Path:
     return exe
 
 
+def build_tools() -> dict:
+    """The reference's two serial programs, built with its Makefile's own commands (Makefile:23-27):
+    {"conv2bin": path, "numCheckSeq": path}.  Raises RuntimeError with the reason otherwise."""
+    dst = REF_DST / "SpComm3D"
+    if not (dst / "src" / "core_ops.cpp").exists():
+        src = find_reference()
+        if src is None:
+            raise RuntimeError("reference sources not found")
+        REF_DST.mkdir(exist_ok=True)
+        shutil.copytree(src, dst, dirs_exist_ok=True)
+    out = {}
+    for name, cmd in (("conv2bin", ["g++", "-w", "-o", str(REF_DST / "ref_conv2bin"),
+                                    str(dst / "tools" / "read_convert_mm.cpp"), f"-I{dst / 'src'}"]),
+                      ("numCheckSeq", ["g++", "-w", "-O3", "-o", str(REF_DST / "ref_numCheckSeq"),
+                                       str(dst / "miniapp" / "numCheckSeq.cpp"), str(dst / "src" / "core_ops.cpp"),
+                                       f"-I{dst / 'src'}"])):
+        exe = Path(cmd[cmd.index("-o") + 1])
+        if not exe.exists():
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"reference {name} build failed: " + res.stderr[-600:].replace("\n", " | "))
+        out[name] = exe
+    return out
+
+
 if __name__ == "__main__":
     print(build(verbose=True))
+    print(build_tools())
