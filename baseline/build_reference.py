@@ -50,7 +50,8 @@ def build(verbose=False) -> Path:
 
 def build_tools() -> dict:
     """The reference's two serial programs, built with its Makefile's own commands (Makefile:23-27):
-    {"conv2bin": path, "numCheckSeq": path}.  Raises RuntimeError with the reason otherwise."""
+    {"conv2bin": path, "numCheckSeq": path}, plus "spmm_check": baseline/ref_spmm_check.cpp linked with the
+    reference's SpMM loop.  Raises RuntimeError with the reason otherwise."""
     dst = REF_DST / "SpComm3D"
     if not (dst / "src" / "core_ops.cpp").exists():
         src = find_reference()
@@ -63,7 +64,11 @@ def build_tools() -> dict:
                                     str(dst / "tools" / "read_convert_mm.cpp"), f"-I{dst / 'src'}"]),
                       ("numCheckSeq", ["g++", "-w", "-O3", "-o", str(REF_DST / "ref_numCheckSeq"),
                                        str(dst / "miniapp" / "numCheckSeq.cpp"), str(dst / "src" / "core_ops.cpp"),
-                                       f"-I{dst / 'src'}"])):
+                                       f"-I{dst / 'src'}"]),
+                      # the reference's SpMM loop and reader behind a few lines of our own (ref_spmm_check.cpp)
+                      ("spmm_check", ["g++", "-w", "-O3", "-o", str(REF_DST / "ref_spmm_check"),
+                                      str(HERE / "ref_spmm_check.cpp"), str(dst / "src" / "core_ops.cpp"),
+                                      f"-I{dst / 'src'}"])):
         exe = Path(cmd[cmd.index("-o") + 1])
         if not exe.exists():
             res = subprocess.run(cmd, capture_output=True, text=True)

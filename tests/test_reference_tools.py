@@ -83,3 +83,30 @@ def test_sddmm_checksum_agrees_with_the_reference_oracle(ref_tools, tmp_path, k)
         assert res.returncode == 0, res.stderr
         ours = float(res.stdout.strip().splitlines()[-1].rsplit("=", 1)[1])
         assert ours == pytest.approx(ref, rel=2e-5, abs=1e-12), (mtx.name, ours, ref)
+
+
+@pytest.mark.parametrize("k", [8, 20])
+def test_spmm_agrees_with_the_reference_loop(ref_tools, tmp_path, k):
+    """The reference's SpMM loop (src/core_ops.cpp:24-35, behind baseline/ref_spmm_check.cpp) against our CPU
+    kernel and the fp64 oracle on the same files, read by the respective readers."""
+    import torch
+    from spcomm3d_b200.ops import local, oracle
+    from spcomm3d_b200.utils import binfmt
+    for mtx in _cases(tmp_path):
+        res = subprocess.run([str(ref_tools["spmm_check"]), str(k), str(mtx)], capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+        ref_sum, ref_sq = (float(x) for x in res.stdout.split())
+        m = binfmt.read_mtx(str(mtx))
+        X = (torch.arange(m.ncols, dtype=torch.float64) % 97)[:, None] / 100 + \
+            torch.arange(k, dtype=torch.float64)[None, :] / 1000
+        y_oracle = oracle.spmm_ref(m, X)
+        order = np.lexsort((m.cols, m.rows))
+        rows, cols, vals = m.rows[order], m.cols[order], m.vals[order]
+        rowptr = np.zeros(m.nrows + 1, np.int64)
+        np.cumsum(np.bincount(rows, minlength=m.nrows), out=rowptr[1:])
+        Y = torch.zeros(m.nrows, k, dtype=torch.float64)
+        local.spmm(torch.from_numpy(rowptr), torch.from_numpy(rows.astype(np.int32)),
+                   torch.from_numpy(cols.astype(np.int32)), torch.from_numpy(vals), X, Y, 0.0)
+        for y in (y_oracle, Y):
+            assert float(y.sum()) == pytest.approx(ref_sum, rel=1e-9, abs=1e-9), mtx.name
+            assert float((y * y).sum()) == pytest.approx(ref_sq, rel=1e-9), mtx.name
