@@ -58,7 +58,8 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
                 assert err <= 2e-5 * max(1.0, yref.abs().max()) * 8, (variant, "spmm", float(err))
     # Z reduction inside the NVSwitch (multimem.ld_reduce over a multicast-bound buffer of the fiber).  No rank
     # raises while the buffer is bound: errors are collected, agreed on, and reported after the release.
-    if mesh.Z > 1:
+    # Exercised where the fiber is the whole job (1x1xZ): multicast objects over sub-groups are not verified yet.
+    if mesh.Z > 1 and mesh.Z == world:
         import torch.distributed as dist
         bad = torch.zeros(1, device=dev)
         sd = None
