@@ -57,6 +57,24 @@ def test_bench_cli_under_torchrun_prints_parsable_lines(tmp_path):
     assert sum(l.startswith("web ") for l in out.stdout.splitlines()) == 3 * 2
 
 
+def test_sweep_cli_reports_every_mesh_and_variant():
+    import json
+    out = _torchrun(2, "spcomm3d_b200.cli.sweep", "--gen", "zipf:900:1200:1.5:200", "-k", "16", "--meshes",
+                    "2x1x1,1x2x1,1x1x2,2x2x1", "--variants", "sparseNRB,dense,fused", "--steps", "2", "--warmup", "1",
+                    "--device", "cpu")
+    assert out.returncode == 0, out.stderr[-2000:]
+    recs = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    # three 2-rank meshes (2x2x1 is skipped) x two CPU variants (fused needs GPUs) x two kernels
+    assert len(recs) == 3 * 2 * 2
+    assert {r["mesh"] for r in recs} == {"2x1x1", "1x2x1", "1x1x2"}
+    by = {(r["mesh"], r["variant"], r["kernel"]): r for r in recs}
+    for mesh in ("2x1x1", "1x2x1"):
+        for kern in ("sddmm", "spmm"):
+            assert by[(mesh, "sparseNRB", kern)]["comm_bytes_total"] <= by[(mesh, "dense", kern)]["comm_bytes_total"]
+    for r in recs:
+        assert r["ms"] > 0 and r["roofline"]["floor_ms"] >= 0 and r["roofline"]["bound"] in ("nvlink", "hbm", "flops")
+
+
 def test_checksum_tools_agree(tmp_path):
     from spcomm3d_b200.cli import num_check_seq
     m = generate.fixed_degree(300, 300, 4, seed=2)
