@@ -33,7 +33,7 @@ def base_parser(prog: str, description: str) -> argparse.ArgumentParser:
     ap.add_argument("--variant", "--variants", dest="variant", default=None,
                     help="comma list of sparse,sparseNRB,fused,fused-atomic,fused-multimem,dense")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--gen", default=None, help="synthetic matrix: uniform:M:N:deg | rmat:scale[:ef] | zipf:M:N[:a[:dmax]] | er:M:N:deg")
+    ap.add_argument("--gen", default=None, help="synthetic matrix: uniform:M:N:deg | rmat:scale[:ef] | zipf:M:N[:a[:dmax]] | er:M:N:deg | random:M:N:nnz")
     ap.add_argument("--device", default=None, choices=["cpu", "cuda"])
     ap.add_argument("--policy", default="respect_comm", choices=["respect_comm", "random"])
     ap.add_argument("--json", action="store_true", help="also print one JSON record per instance")

@@ -70,10 +70,30 @@ def rmat(scale: int, edge_factor: int = 16, a: float = 0.57, b: float = 0.19, c:
     return CooMatrix(n, n, rows, cols, vals, name=f"rmat_s{scale}_ef{edge_factor}")
 
 
+def random_nnz(nrows: int, ncols: int, nnz: int, seed: int = 0) -> CooMatrix:
+    """Exactly `nnz` distinct positions drawn uniformly, every value 1.0, sorted by (row, col): the seeded
+    counterpart of the reference's COOMatrix::self_generate_random (src/SparseMatrix.hpp:49-67, which seeds
+    from the clock)."""
+    total = nrows * ncols
+    if not 0 <= nnz <= total:
+        raise ValueError(f"cannot place {nnz} distinct nonzeros in a {nrows} x {ncols} matrix")
+    rng = np.random.Generator(np.random.Philox(seed))
+    keys = np.zeros(0, np.int64)
+    while keys.size < nnz:
+        draw = rng.integers(0, total, size=int((nnz - keys.size) * 1.1) + 16, dtype=np.int64)
+        keys = np.union1d(keys, draw)
+    if keys.size > nnz:
+        keys = np.sort(rng.choice(keys, nnz, replace=False))
+    return CooMatrix(nrows, ncols, (keys // ncols).astype(np.uint32), (keys % ncols).astype(np.uint32),
+                     np.ones(nnz, np.float64), name=f"random_{nrows}x{ncols}_nnz{nnz}")
+
+
 def from_spec(spec: str, seed: int = 0) -> CooMatrix:
     """Parses `uniform:M:N:deg`, `rmat:scale[:ef]`, `zipf:M:N[:alpha[:dmax]]`,
-    `er:M:N:mean_degree`."""
+    `er:M:N:mean_degree`, `random:M:N:nnz`."""
     kind, *args = spec.split(":")
+    if kind == "random":
+        return random_nnz(int(args[0]), int(args[1]), int(args[2]), seed)
     if kind == "uniform":
         return fixed_degree(int(args[0]), int(args[1]), int(args[2]), seed)
     if kind == "rmat":

@@ -78,3 +78,16 @@ def test_k_and_nnz_splits():
         assert all(o + w == parts[i + 1][0] for i, (o, w) in enumerate(parts[:-1]))
         assert [w for _, w in parts] == [k // Z + (1 if z < k % Z else 0) for z in range(Z)]
     assert split_nnz(10, 4, 1) == (3, 3) and split_nnz(10, 4, 3) == (8, 2)
+
+
+def test_random_nnz_exact_count_unique_and_seeded():
+    a = generate.random_nnz(300, 200, 5000, seed=4)
+    b = generate.from_spec("random:300:200:5000", seed=4)
+    c = generate.random_nnz(300, 200, 5000, seed=5)
+    assert a.nnz == 5000 and np.all(a.vals == 1.0)
+    keys = a.rows.astype(np.int64) * 200 + a.cols
+    assert np.all(np.diff(keys) > 0) and a.rows.max() < 300 and a.cols.max() < 200
+    assert np.array_equal(a.rows, b.rows) and np.array_equal(a.cols, b.cols)
+    assert not (np.array_equal(a.rows, c.rows) and np.array_equal(a.cols, c.cols))
+    full = generate.random_nnz(7, 9, 63, seed=1)
+    assert full.nnz == 63
