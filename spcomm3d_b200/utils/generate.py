@@ -71,21 +71,11 @@ def rmat(scale: int, edge_factor: int = 16, a: float = 0.57, b: float = 0.19, c:
 
 
 def random_nnz(nrows: int, ncols: int, nnz: int, seed: int = 0) -> CooMatrix:
-    """Exactly `nnz` distinct positions drawn uniformly, every value 1.0, sorted by (row, col): the seeded
-    counterpart of the reference's COOMatrix::self_generate_random (src/SparseMatrix.hpp:49-67, which seeds
-    from the clock)."""
-    total = nrows * ncols
-    if not 0 <= nnz <= total:
-        raise ValueError(f"cannot place {nnz} distinct nonzeros in a {nrows} x {ncols} matrix")
-    rng = np.random.Generator(np.random.Philox(seed))
-    keys = np.zeros(0, np.int64)
-    while keys.size < nnz:
-        draw = rng.integers(0, total, size=int((nnz - keys.size) * 1.1) + 16, dtype=np.int64)
-        keys = np.union1d(keys, draw)
-    if keys.size > nnz:
-        keys = np.sort(rng.choice(keys, nnz, replace=False))
-    return CooMatrix(nrows, ncols, (keys // ncols).astype(np.uint32), (keys % ncols).astype(np.uint32),
-                     np.ones(nnz, np.float64), name=f"random_{nrows}x{ncols}_nnz{nnz}")
+    """Exactly `nnz` distinct positions drawn uniformly, every value 1.0, sorted by (row, col)
+    (`CooMatrix.random_unique`; the reference's COOMatrix::self_generate_random, src/SparseMatrix.hpp:49-67)."""
+    m = CooMatrix.random_unique(nrows, ncols, nnz, seed)
+    m.name = f"random_{nrows}x{ncols}_nnz{nnz}"
+    return m
 
 
 def from_spec(spec: str, seed: int = 0) -> CooMatrix:
