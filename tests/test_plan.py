@@ -126,3 +126,30 @@ def test_directory_is_deterministic_and_seeded():
     assert np.array_equal(a.rowmap, b.rowmap) and np.array_equal(a.row_owner, b.row_owner)
     assert not np.array_equal(a.rowmap, c.rowmap)
     assert np.array_equal(a.rpvec() // 2, a.rowmap)  # owner's mesh row is the row's mesh row
+
+
+@pytest.mark.parametrize("meshstr", ["1x1x1", "2x2x2", "4x2x1", "1x1x8", "3x1x2"])
+def test_degenerate_matrices(meshstr):
+    """No nonzeros at all, a 1 x 1 matrix, fewer rows than mesh rows: plans build, blocks may be empty, and the
+    CPU kernels accept them."""
+    import torch
+    from spcomm3d_b200.ops import local
+    cases = [CooMatrix(10, 12, np.zeros(0), np.zeros(0), np.zeros(0)),
+             CooMatrix(1, 1, [0], [0], [2.0]),
+             CooMatrix(3, 50, [0, 1, 2, 2], [4, 7, 9, 49], [1.0, 2.0, 3.0, 4.0])]
+    mesh = Mesh3D.parse(meshstr)
+    for m in cases:
+        _, plans = build_all_plans(m, mesh, seed=1)
+        assert sum(p.nnz for p in plans.values()) == m.nnz * mesh.Z
+        total = 0.0
+        for p in plans.values():
+            k = 8
+            A = torch.ones(p.row.n_local, k, dtype=torch.float64)
+            B = torch.ones(p.col.n_local, k, dtype=torch.float64)
+            c = local.sddmm(torch.from_numpy(p.rowidx), torch.from_numpy(p.colidx), torch.from_numpy(p.vals), A, B)
+            y = torch.zeros(p.row.n_local, k, dtype=torch.float64)
+            local.spmm(torch.from_numpy(p.rowptr), torch.from_numpy(p.rowidx), torch.from_numpy(p.colidx),
+                       torch.from_numpy(p.vals), B, y, 0.0)
+            if p.coords[2] == 0:
+                total += float(c.sum())
+        assert total == pytest.approx(8 * float(m.vals.sum()))
