@@ -131,3 +131,34 @@ def _config1_rank(rank, world):
 
 def test_baseline_config1_and_chain():
     run_ranks(_config1_rank, 8)
+
+
+def _degenerate_rank(rank, world, which):
+    import torch.distributed as dist
+    from spcomm3d_b200.models.dist_ops import DistSDDMM, DistSpMM
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups
+    from spcomm3d_b200.parallel.plan import build_my_plan
+    from spcomm3d_b200.utils.sparse import CooMatrix
+    m = [CooMatrix(10, 12, np.zeros(0), np.zeros(0), np.zeros(0), name="empty"),
+         CooMatrix(1, 1, [0], [0], [2.0], name="one"),
+         CooMatrix(3, 50, [0, 1, 2, 2], [4, 7, 9, 49], [1.0, 2.0, 3.0, 4.0], name="thin")][which]
+    mesh = Mesh3D(2, 1, 2)
+    groups = MeshGroups.create(mesh)
+    _, plan = build_my_plan(m, mesh, rank, seed=1)
+    k = 6
+    for variant in ("sparse", "sparseNRB", "dense"):
+        sd = DistSDDMM(plan, groups, k, torch.float64, "cpu", variant)
+        sd.A_owned.fill_(1.0)
+        sd.B_owned.fill_(1.0)
+        sp = DistSpMM(plan, groups, k, torch.float64, "cpu", variant)
+        sp.X_owned.fill_(1.0)
+        tot = torch.tensor([float(sd.run().sum()), float(sp.run().sum())], dtype=torch.float64)
+        dist.all_reduce(tot)
+        # all-ones operands: every nonzero contributes k * value, once over the whole mesh
+        assert tot.tolist() == pytest.approx([k * float(m.vals.sum())] * 2), (variant, tot.tolist())
+
+
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_degenerate_matrices_distributed(which):
+    """No nonzeros, a 1 x 1 matrix, fewer rows than ranks: most blocks and exchanges are empty."""
+    run_ranks(_degenerate_rank, 4, which)
