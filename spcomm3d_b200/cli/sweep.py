@@ -25,8 +25,8 @@ from ..parallel.plan import build_my_plan
 from ..utils import generate, stats
 from .common import Runtime, base_parser, klist
 
-NVLINK_GBS = 770.0   # measured peer-copy bandwidth per direction on this class of box
-HBM_GBS = 6549.8     # measured copy bandwidth
+_PEAKS = stats.measured_peaks()   # roofline denominators: measured copy bandwidth, measured NVLink peer copy
+NVLINK_GBS, HBM_GBS = _PEAKS["nvlink_gbs"], _PEAKS["hbm_gbs"]
 
 
 def main(argv=None):

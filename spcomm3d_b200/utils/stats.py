@@ -79,6 +79,22 @@ def report_iteration(op, groups=None, rank: int = 0, out=print):
     return aggs
 
 
+def measured_peaks() -> dict:
+    """{"hbm_gbs", "nvlink_gbs", "source"}: the copy bandwidth measured on this pool's GPUs if a
+    MEASURED_PEAKS.json lies at the repository root (key `hbm_gbs`), else 6549.8 GB/s from an earlier
+    measurement; 770 GB/s per direction for a peer copy over NVLink (measured on the same class of box)."""
+    from pathlib import Path
+    out = {"hbm_gbs": 6549.8, "nvlink_gbs": 770.0, "source": "built-in (earlier measurement)"}
+    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    try:
+        d = json.loads(f.read_text())
+        if float(d.get("hbm_gbs", 0)) > 0:
+            out["hbm_gbs"], out["source"] = float(d["hbm_gbs"]), f.name
+    except (OSError, ValueError):
+        pass
+    return out
+
+
 def roofline(flops: float, nvlink_bytes_per_rank: float, hbm_bytes_per_rank: float, ms: float,
              peak_tflops: float = 70.0, nvlink_gbs: float = 770.0, hbm_gbs: float = 6549.8) -> dict:
     """Time floor of a fused op = the slowest of its FLOPs at peak, its NVLink
