@@ -9,10 +9,18 @@ fp32, synthetic seeded operands -- the SDDMM and SpMM configurations named for
 the 8-GPU comparison.  The total work is fixed as N grows (strong scaling).
 `value` is milliseconds per step, device-timed with CUDA events, max over
 ranks; lower is better.  Extra keys give the per-kernel times, GFLOP/s
-(2*nnz*k per kernel), the communication volume of the plan and the end-to-end
-time of the same step through the public API including the host->device copy
-of the dense operands from pinned memory and the device->host read of the two
-result checksums.
+(2*nnz*k per kernel), the communication volume of the plan, the in-kernel phase
+stamps of the fused kernels next to the plain local kernels on the same
+blocks, and the end-to-end time of the same step through the public API
+including the host->device copy of the dense operands from pinned memory and
+the device->host read of the two result checksums.
+
+The run checks itself: after every loop all ranks read the status words of
+the fused kernels (a wait that ran out or a bad index stops the job without a
+number), every rank recomputes a sample of the SDDMM values and SpMM rows it
+owns in fp64 from the seeded operand generator (`verified`, `max_rel_err`),
+and the two result checksums are summed over all ranks so that they can be
+compared across GPU counts and meshes.
 
 Operands are larger than the L2 cache at every N (>= 0.5 GB per rank), so no
 L2 flush is interleaved; `config.l2` states this.
@@ -46,6 +54,9 @@ def parse_args():
     ap.add_argument("--panels", action="store_true",
                     help="SDDMM and SpMM: dense 128x64 panels on the tcgen05 tensor cores (TF32), rest on the gather kernels")
     ap.add_argument("--min-col-nnz", type=int, default=3)
+    ap.add_argument("--no-local", action="store_true", help="skip timing the plain local kernels on each rank's block")
+    ap.add_argument("--save-plan", default=None, metavar="PREFIX", help="write every rank's plan to PREFIX.rank<r>.npz")
+    ap.add_argument("--load-plan", default=None, metavar="PREFIX", help="read plans written by --save-plan instead of building them")
     return ap.parse_args()
 
 
@@ -122,18 +133,38 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+METRIC = "SDDMM+SpMM ms/iter (max over ranks)"
+UNIT = "ms/iter"
+STREAM_A, STREAM_B = 1, 2   # operand streams of models.layer.SddmmSpmmStep
+VERIFY_TOL = 1e-4           # sampled results against fp64, relative to the largest reference value
+
+
+def pick_device(local_rank: int, world: int) -> int:
+    """CUDA device of a rank.  With more visible GPUs than ranks the ranks are spread over the node
+    (rank r -> device r * visible / world) so that neighbouring ranks do not share a PCIe uplink for their
+    host->device copies; SP3_DEVICE_MAP=dense keeps rank r on device r."""
+    import torch
+    visible = torch.cuda.device_count()
+    if os.environ.get("SP3_DEVICE_MAP", "spread") == "spread" and visible > world and visible % world == 0:
+        return local_rank * (visible // world)
+    return local_rank
+
+
 def run_ours(args):
     # torchrun pins OMP_NUM_THREADS to 1; matrix generation and plan building (host library, OpenMP) are setup
     # work outside the timed region and may use this rank's share of the cores
     world_env = int(os.environ.get("WORLD_SIZE", 1))
     if os.environ.get("OMP_NUM_THREADS") == "1" and world_env > 1:
         os.environ["OMP_NUM_THREADS"] = str(max(1, min(16, (os.cpu_count() or 1) // world_env)))
+    import numpy as np
     import torch
     import torch.distributed as dist
+    from spcomm3d_b200.models import verify
     from spcomm3d_b200.models.layer import SddmmSpmmStep
     from spcomm3d_b200.ops import cuda_ops
-    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups, dims_create
-    from spcomm3d_b200.parallel.plan import build_my_plan
+    from spcomm3d_b200.parallel import health
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups
+    from spcomm3d_b200.parallel.plan import RankPlan, build_my_plan
     from spcomm3d_b200.utils import generate, native
 
     rank = int(os.environ.get("RANK", 0))
@@ -141,25 +172,36 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
+    dev_index = pick_device(local_rank, world)
+    torch.cuda.set_device(dev_index)
+    device = torch.device("cuda", dev_index)
     native.cuda()
     groups = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # NCCL moves device tensors; gloo serves the host-side collectives of setup (plan fingerprints)
+        dist.init_process_group("cpu:gloo,cuda:nccl", device_id=device)
     mesh = Mesh3D.parse(args.mesh) if args.mesh else Mesh3D(*default_mesh(world))
     if mesh.size != world:
         raise SystemExit(f"mesh {mesh} does not match {world} ranks")
     if world > 1:
         groups = MeshGroups.create(mesh)
     variant = args.variant or ("fused" if world > 1 else "sparseNRB")
+    if variant == "fused-multimem" and mesh.Z != world:
+        raise SystemExit("fused-multimem is limited to meshes whose Z fiber is the whole job (1x1xZ)")
 
     t0 = time.time()
     m = generate.from_spec(args.gen, seed=args.seed)
-    directory, plan = build_my_plan(m, mesh, rank, seed=args.seed)
+    gen_s = time.time() - t0
+    if args.load_plan:
+        plan = RankPlan.load(f"{args.load_plan}.rank{rank}")
+    else:
+        _, plan = build_my_plan(m, mesh, rank, seed=args.seed)
+    if args.save_plan:
+        plan.save(f"{args.save_plan}.rank{rank}")
     gnnz = m.nnz
-    del m
     setup_s = time.time() - t0
+    if world > 1:
+        health.check_consistent(plan, groups)   # same matrix, mesh and seed on every rank, before any launch
     kw = {"panels": True, "min_col_nnz": args.min_col_nnz} if args.panels else {}
     step = SddmmSpmmStep(plan, groups, args.k, torch.float32, device, variant, seed=args.seed, **kw)
     if args.panels and step.sddmm._panels is not None and rank == 0:
@@ -172,32 +214,78 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def maxr(x):
-        t = torch.tensor([x], dtype=torch.float64, device=device)
+    def reduce(values, op):
+        t = torch.tensor(list(values), dtype=torch.float64, device=device)
         if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
+            dist.all_reduce(t, op=op)
+        return t.tolist()
+
+    def maxr(x):
+        return reduce([x], dist.ReduceOp.MAX)[0]
+
+    def agree_healthy(where: str):
+        """Reads the status words of the fused kernels on every rank; one failing rank stops the whole job
+        with its message (no number is printed for a run whose kernels did not complete)."""
+        msg = ""
+        try:
+            step.check()
+        except Exception as e:
+            msg = f"rank {rank} {where}: {e}"
+        if maxr(1.0 if msg else 0.0) > 0:
+            if msg:
+                print(msg, file=sys.stderr)
+            try:
+                step.close()
+            except Exception:
+                pass
+            raise SystemExit(f"bench aborted: a fused kernel reported a failure {where}")
 
     # ---- kernel-path timing: operands resident on the device --------------
     for _ in range(args.warmup):
         step.run_device()
     barrier()
+    agree_healthy("after warm-up")
     launches0 = cuda_ops.LAUNCHES
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
-    with ClockSampler(local_rank) as clocks:
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    with ClockSampler(dev_index) as clocks:
         ev[0].record()
         for i in range(args.steps):
             step.sddmm.run_async()
-            ev[3 * i + 1].record()
+            ev[2 * i + 1].record()
             step.spmm.run_async()
-            ev[3 * i + 2].record()
-            ev[3 * i + 3].record()
+            ev[2 * i + 2].record()
         barrier()
     launches = cuda_ops.LAUNCHES - launches0
+    agree_healthy("in the timed loop")
     total_ms = maxr(ev[0].elapsed_time(ev[-1]))
-    sddmm_ms = maxr(sum(ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(args.steps)) / args.steps)
-    spmm_ms = maxr(sum(ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(args.steps)) / args.steps)
+    sddmm_ms = maxr(sum(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)) / args.steps)
+    spmm_ms = maxr(sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)) / args.steps)
     ms_per_step = total_ms / args.steps
+
+    # in-kernel phase stamps of the last fused launches and the plain local kernels on the same blocks
+    phases = None
+    ph = step.phase_ms()
+    if ph is not None:
+        flat = [ph[op][key] for op in ("sddmm", "spmm") for key in ("pull", "main", "total")]
+        flat = reduce(flat, dist.ReduceOp.MAX)
+        phases = {op: {key: round(flat[3 * i + j], 4) for j, key in enumerate(("pull", "main", "total"))}
+                  for i, op in enumerate(("sddmm", "spmm"))}
+    local_ms = None
+    if world > 1 and not args.no_local:
+        lsd, lsp = step.local_kernel_ms()
+        lsd, lsp = reduce([lsd, lsp], dist.ReduceOp.MAX)
+        local_ms = {"sddmm": round(lsd, 4), "spmm": round(lsp, 4),
+                    "note": "plain local kernels on each rank's block with all dense rows resident, max over ranks"}
+
+    # ---- correctness: a sample of every rank's results against fp64, and global checksums ----
+    c, y = step.run_device()
+    agree_healthy("in the verification step")
+    err_sd = verify.sample_sddmm_error(plan, c, args.k, args.seed, STREAM_A, STREAM_B)
+    err_sp = verify.sample_spmm_error(plan, m, y, args.k, args.seed, STREAM_B)
+    del m
+    err_sd, err_sp = reduce([err_sd, err_sp], dist.ReduceOp.MAX)
+    sums = reduce([float(cuda_ops.checksum(c)), float(cuda_ops.checksum(y.reshape(-1)))], dist.ReduceOp.SUM)
+    verified = bool(err_sd < VERIFY_TOL and err_sp < VERIFY_TOL and np.isfinite(sums).all())
 
     # ---- end to end through the public API ---------------------------------
     e2e = None
@@ -212,41 +300,50 @@ def run_ours(args):
             res = step.run_e2e()
         b.record()
         barrier()
+        agree_healthy("in the end-to-end loop")
         e2e_ms = maxr(a.elapsed_time(b)) / args.steps
-        e2e = {"value": e2e_ms, "unit": "ms/iter (SDDMM+SpMM, incl. H2D of A and B from pinned memory + D2H of the two checksums)",
+        gsum = reduce(res, dist.ReduceOp.SUM)
+        e2e = {"value": e2e_ms, "unit": UNIT,
+               "note": "SDDMM+SpMM incl. H2D of A and B from pinned memory and D2H of the two result checksums, every step",
                "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes,
-               "checksums": [float(x) for x in res]}
+               "global_checksums": gsum,
+               "checksums_match_device_path": bool(np.allclose(gsum, sums, rtol=1e-6, atol=1e-3))}
 
-    vol = step.comm_volume_bytes()
-    vol_t = torch.tensor(vol, dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(vol_t)
+    vol_t = reduce(step.comm_volume_bytes(), dist.ReduceOp.SUM)
     flops = 2.0 * gnnz * args.k
     out = {
-        "metric": "SDDMM+SpMM ms/iter (device-timed, max over ranks)",
-        "value": ms_per_step, "unit": "ms/iter", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-        "dtype": "fp32", "data": "synthetic", "impl": "ours",
+        "metric": METRIC, "value": ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "ours",
+        "timed": "CUDA events on the launching stream, max over ranks",
         "sddmm_ms": sddmm_ms, "spmm_ms": spmm_ms,
         "sddmm_gflops": flops / sddmm_ms / 1e6, "spmm_gflops": flops / spmm_ms / 1e6,
-        "comm_bytes_per_step": {"sddmm_expand": vol_t[0].item(), "sddmm_zreduce": vol_t[1].item(),
-                                "spmm_expand": vol_t[2].item(), "spmm_reduce": vol_t[3].item()},
+        "comm_bytes_per_step": {"sddmm_expand": vol_t[0], "sddmm_zreduce": vol_t[1],
+                                "spmm_expand": vol_t[2], "spmm_reduce": vol_t[3]},
+        "verified": verified, "max_rel_err": {"sddmm": err_sd, "spmm": err_sp},
+        "global_checksums": {"sddmm": sums[0], "spmm": sums[1]},
+        "fused_phase_ms": phases, "local_kernel_ms": local_ms,
         "gpu_launches": launches, "clocks": clocks.summary(), "e2e": e2e,
         "config": {"model": f"{args.gen} k={args.k} fp32 SDDMM then SpMM", "matrix": args.gen, "nnz": gnnz,
                    "k": args.k, "mesh": str(mesh), "variant": variant, "precision": "tf32 panels + fp32" if args.panels else "fp32", "global_batch": None, "seq_len": None,
                    "parallelism": f"mesh{mesh}", "l2": "operands larger than L2 at every N; no flush",
-                   "setup_s": round(setup_s, 1)},
+                   "device_of_rank0": dev_index, "setup_s": round(setup_s, 1), "generate_s": round(gen_s, 1)},
     }
+    if not verified:
+        print(f"verification FAILED: max rel err sddmm {err_sd:.3e}, spmm {err_sp:.3e}", file=sys.stderr)
     if rank == 0:
         print(json.dumps(out))
+    step.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not verified:
+        raise SystemExit(3)
 
 
 def run_reference(args):
     from baseline import reference_arm
-    reference_arm.run(args)
+    reference_arm.run(args, METRIC, UNIT)
 
 
 if __name__ == "__main__":

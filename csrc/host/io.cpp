@@ -18,6 +18,7 @@
 #include <string>
 #include <sys/stat.h>
 #include <unistd.h>
+#include <new>
 #include <vector>
 
 namespace {
@@ -47,7 +48,9 @@ SP3_API int sp3_bin_read_header(const char* path, uint32_t* nrows, uint32_t* nco
     int rc = pread_all(fd, &h, sizeof h, 0);
     struct stat st;
     if (rc == sp3::OK && fstat(fd, &st) == 0) {
-        if ((uint64_t)st.st_size < sizeof(BinHeader) + h.nnz * sizeof(BinTriplet)) rc = sp3::E_FORMAT;
+        // divide instead of multiplying: a corrupt count near 2^64 must not wrap past the check
+        if ((uint64_t)st.st_size < sizeof(BinHeader) ||
+            h.nnz > ((uint64_t)st.st_size - sizeof(BinHeader)) / sizeof(BinTriplet)) rc = sp3::E_FORMAT;
     }
     close(fd);
     if (rc != sp3::OK) return rc;
@@ -63,9 +66,13 @@ SP3_API int sp3_bin_read_range(const char* path, uint64_t start, uint64_t count,
     if (fd < 0) return sp3::E_IO;
     BinHeader h;
     int rc = pread_all(fd, &h, sizeof h, 0);
-    if (rc == sp3::OK && start + count > h.nnz) rc = sp3::E_RANGE;
+    if (rc == sp3::OK && (start > h.nnz || count > h.nnz - start)) rc = sp3::E_RANGE;
     const size_t CH = 1u << 20;
-    std::vector<BinTriplet> buf(count < CH ? (size_t)count : CH);
+    std::vector<BinTriplet> buf;
+    if (rc == sp3::OK) {
+        try { buf.resize(count < CH ? (size_t)count : CH); }
+        catch (const std::bad_alloc&) { rc = sp3::E_IO; }  // nothing may be thrown across the C interface
+    }
     for (uint64_t done = 0; rc == sp3::OK && done < count;) {
         size_t n = (size_t)((count - done) < CH ? (count - done) : CH);
         rc = pread_all(fd, buf.data(), n * sizeof(BinTriplet),

@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <cstring>
 #include <numeric>
+#include <omp.h>
 #include <vector>
 
 // map[id] = mesh coordinate in [0,parts): seeded Fisher-Yates shuffle of the
@@ -36,18 +37,40 @@ SP3_API int sp3_bucket_blocks(uint64_t nnz, const uint32_t* rows, const uint32_t
                               const int32_t* rowmap, const int32_t* colmap, uint32_t X, uint32_t Y,
                               int64_t* offsets, int64_t* perm) {
     const uint32_t nb = X * Y;
-    std::vector<int64_t> cnt(nb + 1, 0);
-    for (uint64_t i = 0; i < nnz; ++i) {
-        uint32_t b = (uint32_t)rowmap[rows[i]] * Y + (uint32_t)colmap[cols[i]];
-        if (b >= nb) return sp3::E_RANGE;
-        ++cnt[b + 1];
+    // Every thread counts a contiguous piece of the nonzeros; the piece counts, scanned block-major and
+    // thread-minor, give each thread its write positions, so the result is the stable order whatever the
+    // number of threads.
+    const int T = std::max(1, omp_get_max_threads());
+    std::vector<int64_t> cnt((size_t)T * nb, 0);
+    int bad = 0;
+#pragma omp parallel num_threads(T) reduction(| : bad)
+    {
+        const int t = omp_get_thread_num();
+        const uint64_t lo = nnz * (uint64_t)t / T, hi = nnz * (uint64_t)(t + 1) / T;
+        int64_t* c = cnt.data() + (size_t)t * nb;
+        for (uint64_t i = lo; i < hi; ++i) {
+            uint32_t b = (uint32_t)rowmap[rows[i]] * Y + (uint32_t)colmap[cols[i]];
+            if (b >= nb) { bad = 1; break; }
+            ++c[b];
+        }
     }
-    for (uint32_t b = 0; b < nb; ++b) cnt[b + 1] += cnt[b];
-    std::memcpy(offsets, cnt.data(), (nb + 1) * sizeof(int64_t));
+    if (bad) return sp3::E_RANGE;
+    int64_t run = 0;
+    for (uint32_t b = 0; b < nb; ++b) {
+        offsets[b] = run;
+        for (int t = 0; t < T; ++t) { int64_t c = cnt[(size_t)t * nb + b]; cnt[(size_t)t * nb + b] = run; run += c; }
+    }
+    offsets[nb] = run;
     if (!perm) return sp3::OK;
-    for (uint64_t i = 0; i < nnz; ++i) {
-        uint32_t b = (uint32_t)rowmap[rows[i]] * Y + (uint32_t)colmap[cols[i]];
-        perm[cnt[b]++] = (int64_t)i;
+#pragma omp parallel num_threads(T)
+    {
+        const int t = omp_get_thread_num();
+        const uint64_t lo = nnz * (uint64_t)t / T, hi = nnz * (uint64_t)(t + 1) / T;
+        int64_t* c = cnt.data() + (size_t)t * nb;
+        for (uint64_t i = lo; i < hi; ++i) {
+            uint32_t b = (uint32_t)rowmap[rows[i]] * Y + (uint32_t)colmap[cols[i]];
+            perm[c[b]++] = (int64_t)i;
+        }
     }
     return sp3::OK;
 }
@@ -81,25 +104,29 @@ SP3_API int sp3_assign_owners(uint64_t n, const int64_t* mask, const int32_t* li
                               uint32_t nlines, uint32_t parts, int policy, uint64_t seed,
                               uint64_t stream, int32_t* owner, int32_t* pos, int64_t* counts) {
     if (parts == 0 || parts > 62) return sp3::E_ARG;
+    // pass 1 (parallel): the seeded pick among the touching ranks depends on the id alone
+    int bad = 0;
+#pragma omp parallel for schedule(static) reduction(| : bad)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        if ((uint32_t)linemap[i] >= nlines) { bad = 1; owner[i] = -1; continue; }
+        uint64_t m = policy == 1 ? 0 : (uint64_t)mask[i];
+        if (m == 0) { owner[i] = -1; continue; }
+        int pc = __builtin_popcountll(m);
+        int pick = (int)(sp3::rnd(seed, stream, (uint64_t)i) % (uint64_t)pc);
+        uint64_t mm = m;
+        while (pick--) mm &= mm - 1;
+        int o = __builtin_ctzll(mm);
+        if ((uint32_t)o >= parts) { bad = 1; o = -1; }
+        owner[i] = o;
+    }
+    if (bad) return sp3::E_RANGE;
+    // pass 2 (in id order): round-robin for the ids nobody touches, positions inside the owned lists
     std::vector<uint64_t> rr(nlines, 0);
     std::fill(counts, counts + (size_t)nlines * parts, 0);
     for (uint64_t i = 0; i < n; ++i) {
         uint32_t line = (uint32_t)linemap[i];
-        if (line >= nlines) return sp3::E_RANGE;
-        uint64_t m = policy == 1 ? 0 : (uint64_t)mask[i];
-        int32_t o;
-        if (m == 0) {
-            o = (int32_t)(rr[line]++ % parts);
-        } else {
-            int pc = __builtin_popcountll(m);
-            int pick = (int)(sp3::rnd(seed, stream, i) % (uint64_t)pc);
-            uint64_t mm = m;
-            while (pick--) mm &= mm - 1;
-            o = __builtin_ctzll(mm);
-            if ((uint32_t)o >= parts) return sp3::E_RANGE;
-        }
-        owner[i] = o;
-        pos[i] = (int32_t)counts[(size_t)line * parts + o]++;
+        if (owner[i] < 0) owner[i] = (int32_t)(rr[line]++ % parts);
+        pos[i] = (int32_t)counts[(size_t)line * parts + owner[i]]++;
     }
     return sp3::OK;
 }
@@ -132,7 +159,7 @@ SP3_API int sp3_csr_order(uint64_t nnz, const int32_t* lrow, const int32_t* lcol
 SP3_API int sp3_remap_u32(uint64_t n, const uint32_t* idx, const int32_t* table, uint64_t table_len,
                           int32_t* out) {
     int bad = 0;
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) reduction(| : bad)
     for (int64_t i = 0; i < (int64_t)n; ++i) {
         if (idx[i] >= table_len || table[idx[i]] < 0) { bad = 1; out[i] = -1; }
         else out[i] = table[idx[i]];

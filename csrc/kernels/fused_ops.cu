@@ -46,7 +46,9 @@ namespace sp3 {
 
 constexpr int MAX_RANKS = 64;
 enum FlagKind : int { F_READY = 0, F_DONE = 1, F_PART = 2, F_KINDS = 3 };
-enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_TICKET_WORK = 6, C_WORK_DONE = 7, C_TICKET_PUSH = 8, C_TICKET_START = 9, C_START_DONE = 10, C_WORDS = 16 };
+constexpr int MAX_WAVES = 32;
+// words [C_WAVE0, C_WAVE0 + MAX_WAVES): pull tiles finished per wave (see FusedSddmmArgs::wave_nnz)
+enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET_FIN = 3, C_FIN_DONE = 4, C_ABORT = 5, C_TICKET_WORK = 6, C_WORK_DONE = 7, C_TICKET_PUSH = 8, C_TICKET_START = 9, C_START_DONE = 10, C_WAVE0 = 16, C_WORDS = C_WAVE0 + MAX_WAVES };
 enum Phase : int { PH_START = 1, PH_MAIN = 2, PH_FINISH = 4 };
 enum WaitSite : int { W_READY = 1, W_PULLS = 2, W_PART = 3, W_DONE = 4, W_WORK = 5 };
 
@@ -260,6 +262,15 @@ struct FusedSddmmArgs {
     // allocation) with `multimem.ld_reduce.add`, which returns the sum over all fiber ranks.
     const float* mc_part;
     long long part_stride;
+    // Pull waves.  The pull tickets are served in the order pull_order[t] (bit 30 set: tile of needed A rows,
+    // else tile of needed B rows; low bits: tile number; null: A tiles then B tiles) and grouped into n_waves
+    // waves of tiles_per_wave consecutive tickets.  The nonzeros are given sorted by the last wave that brings
+    // one of their two rows (class 0: both rows owned); wave_nnz[c] (c = 0..n_waves) is the number of nonzeros
+    // that can be computed once the first c waves are complete.  A work unit waits only for the waves its own
+    // nonzeros need, so compute follows the pulls wave by wave instead of starting after the last tile.
+    const int* pull_order;
+    int n_waves, tiles_per_wave;
+    const long long* wave_nnz;
 };
 
 // Sum over all devices of a multicast object, added in the NVSwitch (NVLS); `p` is a multicast address.
@@ -333,46 +344,70 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
                                  a.zbase, a.zrem, a.zwidth};
         float4* Bv = reinterpret_cast<float4*>(a.B_loc);
         const long long ldb_v = a.ldb / 4;
-        bool pulled = n_pull == 0, pulls_left = n_pull > 0;
+        bool pulls_left = n_pull > 0;
         const long long n_free_units = a.nnz_free / per_unit;  // units that touch no pulled row
+        const int n_waves = n_pull > 0 ? (a.n_waves > 0 ? a.n_waves : 1) : 0;
+        const int tpw = a.n_waves > 0 ? a.tiles_per_wave : (n_pull > 0 ? n_pull : 1);
         auto pull_one = [&]() -> bool {
             const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
             if (t >= n_pull) return false;
-            if (t < n_pull_a) {
-                const int r0 = t * PULL_ROWS;
+            const int code = a.pull_order ? __ldg(a.pull_order + t) : (t < n_pull_a ? (t | (1 << 30)) : t - n_pull_a);
+            const int tile = code & ((1 << 30) - 1);
+            if (code >> 30) {
+                const int r0 = tile * PULL_ROWS;
                 const int r1 = r0 + PULL_ROWS < a.n_recv_a ? r0 + PULL_ROWS : a.n_recv_a;
                 pull_rows(r0, r1, a.a_src, reinterpret_cast<float4*>(a.A_stage), ldb_v, a.nvec, lane);
             } else {
-                const int r0 = (t - n_pull_a) * PULL_ROWS;
+                const int r0 = tile * PULL_ROWS;
                 const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
                 pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
             }
             __threadfence();
             __syncwarp();
-            if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
+            if (lane == 0) {
+                atomicAdd(c.ctrl + C_WAVE0 + t / tpw, 1);
+                if (atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
+            }
+            return true;
+        };
+        // Units runnable once the first w waves are complete (w = 0: the units that need no pulled row).
+        auto units_after = [&](int w) -> long long {
+            if (w >= n_waves) return n_units;
+            const long long z = a.wave_nnz ? a.wave_nnz[w] : a.nnz_free;
+            return z >= a.nnz ? n_units : z / per_unit;
+        };
+        int waves_ready = 0;   // leading waves this warp knows to be complete
+        // Makes sure that every wave units [.., u1) need is complete: a warp whose units are not ready serves a
+        // pull ticket (so every ticket is taken by a running warp and the wait cannot deadlock) and looks again;
+        // when no ticket is left it waits, with a time limit, for the warps that still copy.
+        auto ensure_waves = [&](long long u1) -> bool {
+            while (waves_ready < n_waves && u1 > units_after(waves_ready)) {
+                const int w = waves_ready;
+                const int want = (w + 1) * tpw <= n_pull ? tpw : n_pull - w * tpw;
+                if (ld_acquire_gpu(c.ctrl + C_WAVE0 + w) >= want) { ++waves_ready; continue; }
+                if (pulls_left) { pulls_left = pull_one(); continue; }
+                if (!wait_counter(c, C_WAVE0 + w, want, W_PULLS)) return false;
+                ++waves_ready;
+            }
             return true;
         };
         // One warp in four is a puller: it serves pull tickets until none are left (a quarter of the warps,
         // 4 KB of reads in flight each, is enough to fill NVLink) while the others start on the units that
-        // need no pulled row.  A warp that reaches a unit needing pulled rows first helps to finish the pulls
-        // and then waits for them; every pull ticket is thus taken by a running warp and the wait cannot
-        // deadlock.
+        // need no pulled row.
         const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-        if ((gwarp & 3) == 0 || n_free_units == 0)
+        (void)n_free_units;
+        if ((gwarp & 3) == 0)
             while (ok && pulls_left) pulls_left = pull_one();
         const int SDDMM_UNITS_PER_TICKET = per_ticket(n_units, nwarps, SDDMM_UNITS_PER_TICKET_MAX);
         while (ok) {
             const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
             if (u0 >= n_units) break;
             const long long u1 = u0 + SDDMM_UNITS_PER_TICKET < n_units ? u0 + SDDMM_UNITS_PER_TICKET : n_units;
-            if (!pulled && u1 > n_free_units) {
-                while (pulls_left) pulls_left = pull_one();
-                ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
-                pulled = true;
-                if (!ok) break;
-            }
+            ok = ensure_waves(u1);
+            if (!ok) break;
             for (long long u = u0; u < u1; ++u)
-                sddmm_warp_unit<float, G, R, U>(u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
+                sddmm_warp_unit<float, G, R, U, RowsByPeerRef<float>, StorePartial, false>(
+                    u, a.nnz, a.rowidx, a.colidx, arows, Bv, ldb_v, a.nvec, store, lane);
             if (self_push) {
                 // the values [i0, i1) of `part` were written by this warp just now (still in L2): send the pieces
                 // that belong to other fiber ranks as contiguous remote stores while other warps compute
@@ -593,6 +628,9 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
         if (!(c.phases & PH_START) && blockIdx.x == 0 && threadIdx.x == 0) stamp(c, T_START);
         bool ok = wait_all(c, F_READY, c.read_from, c.n_read, W_READY);
         if (ATOMIC) ok = wait_all(c, F_READY, c.push_to, c.n_push, W_READY) && ok;
+        // atomic mode, START and MAIN in one launch: my own START warps scale (or clear) the rows that receive
+        // contributions with plain stores; nobody may add into them, me included, before all of them are done
+        if (ATOMIC && (c.phases & PH_START)) ok = wait_counter(c, C_START_DONE, nwarps, W_READY) && ok;
         const int n_pull = (a.n_recv_x + PULL_ROWS - 1) / PULL_ROWS;
         float4* Xv = reinterpret_cast<float4*>(a.X_loc);
         const long long ldx_v = a.ldx / 4;
@@ -623,12 +661,12 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
                 const EmitOwnedOrAdd add{reinterpret_cast<float4*>(a.Y), a.ldy / 4, a.beta, a.n_owned_y, a.y_dst,
                                          a.crow_flag, a.red_v4};
                 for (int it = i0; it < i1; ++it)
-                    spmm_warp_item<float, G, R, U>(__ldg(a.items + it), a.rowptr, a.colidx, a.val, Xv, ldx_v, a.nvec,
-                                                   add, a.lg, lane);
+                    spmm_warp_item<float, G, R, U, EmitOwnedOrAdd, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
+                                                                          Xv, ldx_v, a.nvec, add, a.lg, lane);
             } else {
                 for (int it = i0; it < i1; ++it)
-                    spmm_warp_item<float, G, R, U>(__ldg(a.items + it), a.rowptr, a.colidx, a.val, Xv, ldx_v, a.nvec,
-                                                   emit, a.lg, lane);
+                    spmm_warp_item<float, G, R, U, EmitOwnedOrPush, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
+                                                                           Xv, ldx_v, a.nvec, emit, a.lg, lane);
             }
         }
         main_epilogue(c, lane, nwarps);
@@ -676,19 +714,30 @@ SP3_API int sp3_fused_struct_sizes(int* sddmm_bytes, int* spmm_bytes, int* comm_
     return 0;
 }
 
+// The kernels synchronise their own warps through grid-wide counters, so every block of the grid has to be
+// resident at once.  A cooperative launch gives that guarantee: the grid is sized from the occupancy query and
+// the launch fails with an error (instead of a kernel that waits for blocks that never start) if the device
+// cannot hold it.
+template <typename K, typename A>
+static int launch_resident(K kernel, const A& args, cudaStream_t st) {
+    A copy = args;
+    void* params[] = {&copy};
+    const unsigned blocks = persistent_blocks(kernel, 0);
+    return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(blocks), dim3(256), params, 0, st);
+}
+
 SP3_API int sp3_fused_sddmm_f32(const void* args, void* stream) {
     FusedSddmmArgs a = *reinterpret_cast<const FusedSddmmArgs*>(args);
     cudaStream_t st = (cudaStream_t)stream;
+    if (a.n_waves > MAX_WAVES) return (int)cudaErrorInvalidValue;
     cudaError_t e = cudaMemsetAsync(a.comm.ctrl, 0, C_WORDS * sizeof(int), st);
     if (e != cudaSuccess) return (int)e;
-    int G, R;
+    int G, R, rc = 0;
     pick_shape(a.nvec, &G, &R, false);
-#define SP3_FSDDMM(GG, RR)                                                                       \
-    fused_sddmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>                                                \
-        <<<persistent_blocks(fused_sddmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>, 0), 256, 0, st>>>(a)
+#define SP3_FSDDMM(GG, RR) rc = launch_resident(fused_sddmm_kernel<GG, RR, (RR >= 8 ? 2 : 4)>, a, st)
     SP3_DISPATCH_GR(SP3_FSDDMM)
 #undef SP3_FSDDMM
-    return (int)cudaGetLastError();
+    return rc ? rc : (int)cudaGetLastError();
 }
 
 SP3_API int sp3_fused_spmm_f32(const void* args, void* stream) {
@@ -696,16 +745,15 @@ SP3_API int sp3_fused_spmm_f32(const void* args, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaMemsetAsync(a.comm.ctrl, 0, C_WORDS * sizeof(int), st);
     if (e != cudaSuccess) return (int)e;
-    int G, R;
+    int G, R, rc = 0;
     pick_shape(a.nvec, &G, &R, true);
-#define SP3_FSPMM(GG, RR)                                                                               \
-    if (a.atomic)                                                                                       \
-        fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true>                                              \
-            <<<persistent_blocks(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true>, 0), 256, 0, st>>>(a);  \
-    else                                                                                                \
-        fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false>                                             \
-            <<<persistent_blocks(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false>, 0), 256, 0, st>>>(a)
+#define SP3_FSPMM(GG, RR)                                                                        \
+    rc = a.atomic ? launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true>, a, st)   \
+                  : launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false>, a, st)
     SP3_DISPATCH_GR(SP3_FSPMM)
 #undef SP3_FSPMM
-    return (int)cudaGetLastError();
+    return rc ? rc : (int)cudaGetLastError();
 }
+
+// Number of int32 words the caller must provide as `ctrl`.
+SP3_API int sp3_fused_ctrl_words() { return C_WORDS; }

@@ -427,6 +427,8 @@ SP3_API int sp3_cuda_touch_masks(long long nnz, const int* rows, const int* cols
 // array is part of the loaded library image: every GPU that loads the library
 // holds SP3_NOALLOC_SCRATCH_BYTES of device memory until the process exits.
 // ---------------------------------------------------------------------------
+#include <atomic>
+
 #include "sp3_noalloc.h"
 
 namespace {
@@ -435,8 +437,10 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[SP3_NOALLOC_SCR
 constexpr int NOALLOC_MAX_DEVICES = 64;
 // Device address of g_noalloc_scratch per device ordinal, filled on the first
 // call made with that device current.  In host code the symbol name itself is
-// only a handle; the address has to come from cudaGetSymbolAddress.
-unsigned char* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+// only a handle; the address has to come from cudaGetSymbolAddress.  Atomic
+// because first calls may come from several host threads at once (they would
+// all store the same address).
+std::atomic<unsigned char*> g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
 }  // namespace
 
 SP3_API int sp3_cuda_spmm_f32_noalloc(int nrows, int nitems, const void* items, const long long* rowptr,
@@ -455,13 +459,14 @@ SP3_API int sp3_cuda_spmm_f32_noalloc(int nrows, int nitems, const void* items, 
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return (int)err;
     if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SP3_NOALLOC_E_ARG;
-    if (!g_noalloc_ptr[dev]) {
+    unsigned char* base = g_noalloc_ptr[dev].load(std::memory_order_relaxed);
+    if (!base) {
         void* p = nullptr;
         err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (err != cudaSuccess) return (int)err;
-        g_noalloc_ptr[dev] = (unsigned char*)p;
+        base = (unsigned char*)p;
+        g_noalloc_ptr[dev].store(base, std::memory_order_relaxed);
     }
-    unsigned char* base = g_noalloc_ptr[dev];
     cudaStream_t st = (cudaStream_t)stream;
     if (nlong > 0) {
         // the array keeps whatever the previous call left; counters must start at zero

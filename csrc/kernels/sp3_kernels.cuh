@@ -61,6 +61,16 @@ __device__ __forceinline__ void group_transpose_reduce(T (&v)[N], unsigned gmask
     }
 }
 
+// ---- dense-row loads ----------------------------------------------------------
+// NC = true: the non-coherent read-only path (ld.global.nc), for operands that no thread writes while the
+// kernel runs (the local kernels).  NC = false: an ordinary load.  The fused kernels use it for every dense
+// row, because rows of the pulled part of a block are written by other warps of the same launch; ordinary
+// loads are ordered after the acquire that tells a warp the rows are there, the read-only path is not.
+template <bool NC, typename V> __device__ __forceinline__ V ld_row(const V* p) {
+    if constexpr (NC) return __ldg(p);
+    else return *p;
+}
+
 // ---- row access policies ---------------------------------------------------
 // A policy turns the local row index of a nonzero into a 31-bit *reference*
 // (`ref`, evaluated by every lane for its own nonzero when a batch of indices
@@ -112,7 +122,7 @@ template <typename T> struct StoreLocal {
 // above.  The list is sorted by row, so the A row stays in registers until
 // the row changes.  Results leave as one coalesced store per G nonzeros.
 // ---------------------------------------------------------------------------
-template <typename T, int G, int R, int U, typename ARows, typename Store>
+template <typename T, int G, int R, int U, typename ARows, typename Store, bool NC = true>
 __device__ __forceinline__ void sddmm_warp_unit(long long unit, long long nnz, const int* __restrict__ rowidx,
                                                 const int* __restrict__ colidx, const ARows& arows,
                                                 const typename Vec<T>::type* __restrict__ Bv, long long ldb_v,
@@ -152,7 +162,7 @@ __device__ __forceinline__ void sddmm_warp_unit(long long unit, long long nnz, c
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int v = gl + r * G;
-                    b[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Bv + (long long)cc[u] * ldb_v + v) : vzero((V*)nullptr);
+                    b[u][r] = (cc[u] >= 0 && v < nvec) ? ld_row<NC>(Bv + (long long)cc[u] * ldb_v + v) : vzero((V*)nullptr);
                 }
 #pragma unroll
             for (int u = 0; u < UU; ++u) {
@@ -162,7 +172,7 @@ __device__ __forceinline__ void sddmm_warp_unit(long long unit, long long nnz, c
 #pragma unroll
                     for (int r = 0; r < R; ++r) {
                         const int v = gl + r * G;
-                        a[r] = v < nvec ? __ldg(ap + v) : vzero((V*)nullptr);
+                        a[r] = v < nvec ? ld_row<NC>(ap + v) : vzero((V*)nullptr);
                     }
                 }
                 T d = 0;
@@ -208,7 +218,7 @@ template <typename T> struct EmitLocal {
 // Adds val[q] * X[colidx[q]] for q in [p0, p1) taken in batches of G (one
 // coalesced index/value load per batch, broadcast inside the lane group);
 // consecutive batches of this group are `batch_stride` apart.
-template <typename T, int G, int R, int U>
+template <typename T, int G, int R, int U, bool NC = true>
 __device__ __forceinline__ void spmm_accumulate(typename Vec<T>::type (&acc)[R], long long p0, long long p1,
                                                 int batch_stride, unsigned gmask,
                                                 const int* __restrict__ colidx, const T* __restrict__ val,
@@ -236,7 +246,7 @@ __device__ __forceinline__ void spmm_accumulate(typename Vec<T>::type (&acc)[R],
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int v = gl + r * G;
-                    x[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Xv + (long long)cc[u] * ldx_v + v) : vzero((V*)nullptr);
+                    x[u][r] = (cc[u] >= 0 && v < nvec) ? ld_row<NC>(Xv + (long long)cc[u] * ldx_v + v) : vzero((V*)nullptr);
                 }
 #pragma unroll
             for (int u = 0; u < UU; ++u)
@@ -252,7 +262,7 @@ __device__ __forceinline__ void spmm_accumulate(typename Vec<T>::type (&acc)[R],
 // emitted whenever the stream crosses into the next row.  Rows without
 // nonzeros are emitted too (as zeros).  One lane group runs this alone, so no
 // atomics are involved and the result is reproducible.
-template <typename T, int G, int R, int U, typename Emit>
+template <typename T, int G, int R, int U, typename Emit, bool NC = true>
 __device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long* __restrict__ rowptr,
                                                  const int* __restrict__ colidx, const T* __restrict__ val,
                                                  const typename Vec<T>::type* __restrict__ Xv, long long ldx_v,
@@ -304,7 +314,7 @@ __device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int v = gl + r * G;
-                    x[u][r] = (cc[u] >= 0 && v < nvec) ? __ldg(Xv + (long long)cc[u] * ld + v) : vzero((V*)nullptr);
+                    x[u][r] = (cc[u] >= 0 && v < nvec) ? ld_row<NC>(Xv + (long long)cc[u] * ld + v) : vzero((V*)nullptr);
                 }
 #pragma unroll
             for (int u = 0; u < UU; ++u) {
@@ -328,7 +338,7 @@ __device__ __forceinline__ void spmm_rows_stream(int r0, int r1, const long long
     }
 }
 
-template <typename T, int G, int R, int U, typename Emit>
+template <typename T, int G, int R, int U, typename Emit, bool NC = true>
 __device__ __forceinline__ void spmm_warp_item(const int4 item, const long long* __restrict__ rowptr,
                                                const int* __restrict__ colidx, const T* __restrict__ val,
                                                const typename Vec<T>::type* __restrict__ Xv, long long ldx_v,
@@ -341,7 +351,7 @@ __device__ __forceinline__ void spmm_warp_item(const int4 item, const long long*
         const int nr = item.y - item.x;
         const int r0 = item.x + (int)(((long long)nr * slot) / SLOTS);
         const int r1 = item.x + (int)(((long long)nr * (slot + 1)) / SLOTS);
-        spmm_rows_stream<T, G, R, U>(r0, r1, rowptr, colidx, val, Xv, ldx_v, emit, gmask, gl, nvec);
+        spmm_rows_stream<T, G, R, U, Emit, NC>(r0, r1, rowptr, colidx, val, Xv, ldx_v, emit, gmask, gl, nvec);
         return;
     }
     // piece of a long row: the warp reads 32 consecutive entries per step, each
@@ -349,7 +359,7 @@ __device__ __forceinline__ void spmm_warp_item(const int4 item, const long long*
     V acc[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r] = vzero((V*)nullptr);
-    spmm_accumulate<T, G, R, U>(acc, (long long)item.y + slot * G, item.z, 32, gmask, colidx, val, Xv, ldx_v, gl, nvec);
+    spmm_accumulate<T, G, R, U, NC>(acc, (long long)item.y + slot * G, item.z, 32, gmask, colidx, val, Xv, ldx_v, gl, nvec);
 #pragma unroll
     for (int m = G; m < 32; m <<= 1)
 #pragma unroll

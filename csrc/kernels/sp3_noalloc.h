@@ -29,7 +29,10 @@
  *
  * First call.  The first call on each device looks up the device address of
  * the array (cudaGetSymbolAddress) with that device current.  Make that first
- * call outside any CUDA stream capture.
+ * call outside any CUDA stream capture.  First calls may come from several
+ * host threads at once.  `stream` must be a stream of the device that is
+ * current when the function is called (or 0): the array that is used is the
+ * current device's.
  *
  * Sharing.  All calls on one device use the same array.  The counters are
  * cleared at the start of every call (a memset on the given stream), so stale

@@ -28,13 +28,17 @@ def run_instances(rt, plan, args, kernel_cls, default_variants, fill):
                 continue
             fill(op)
             total = 0.0
-            for _ in range(args.iters):
-                rt.barrier()
-                op.run()
-                aggs = stats.report_iteration(op, rt.groups, rt.rank)
-                total += aggs["PRE"]["times"][stats.TIME_KEYS.index("total")]
-            if args.json and rt.rank == 0:
-                print(stats.json_record(op, op.kernel, total / max(1, args.iters)))
+            op.defer_status = True   # a kernel status is raised by close(), after every rank has let go
+            try:
+                for _ in range(args.iters):
+                    rt.barrier()
+                    op.run()
+                    aggs = stats.report_iteration(op, rt.groups, rt.rank)
+                    total += aggs["PRE"]["times"][stats.TIME_KEYS.index("total")]
+                if args.json and rt.rank == 0:
+                    print(stats.json_record(op, op.kernel, total / max(1, args.iters)))
+            finally:
+                op.close()
             del op
 
 

@@ -37,6 +37,10 @@ def base_parser(prog: str, description: str) -> argparse.ArgumentParser:
     ap.add_argument("--device", default=None, choices=["cpu", "cuda"])
     ap.add_argument("--policy", default="respect_comm", choices=["respect_comm", "random"])
     ap.add_argument("--json", action="store_true", help="also print one JSON record per instance")
+    ap.add_argument("--save-plan", default=None, metavar="PREFIX",
+                    help="write every rank's plan to PREFIX.rank<r>.npz after building it")
+    ap.add_argument("--load-plan", default=None, metavar="PREFIX",
+                    help="read the plans written by --save-plan instead of partitioning the matrix again")
     ap.add_argument("-v", dest="verbose", action="store_true")
     return ap
 
@@ -59,7 +63,9 @@ class Runtime:
         if self.world > 1:
             import torch.distributed as dist
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            dist.init_process_group("nccl" if want_cuda else "gloo",
+            # GPU ranks: NCCL for device tensors plus gloo for the host-side collectives of setup (the
+            # collective .bin reader exchanges nonzeros and touch masks as host arrays)
+            dist.init_process_group("cpu:gloo,cuda:nccl" if want_cuda else "gloo",
                                     **({"device_id": self.device} if want_cuda else {}))
         if args.mesh:
             self.mesh = Mesh3D.parse(args.mesh)
@@ -77,11 +83,28 @@ class Runtime:
         v = args.variant.split(",") if args.variant else list(default)
         if self.device.type != "cuda" or self.dtype != torch.float32:
             v = [x for x in v if not x.startswith("fused")]
+        if "fused-multimem" in v and self.mesh.Z != self.world:
+            # a multicast binding over part of the job has not been proven on real switches
+            self.say(f"# skipping fused-multimem on {self.mesh}: limited to meshes whose Z fiber is the whole job")
+            v = [x for x in v if x != "fused-multimem"]
         return v
 
     def load_plan(self, args):
-        """(plan, matrix name).  Generated matrices are built identically on
-        every rank (no communication); files go through the collective reader."""
+        """The plan of this rank.  Generated matrices are built identically on
+        every rank (no communication); files go through the collective reader.
+        --load-plan reads what --save-plan wrote (same mesh and rank count)."""
+        from ..parallel.plan import RankPlan
+        if getattr(args, "load_plan", None):
+            plan = RankPlan.load(f"{args.load_plan}.rank{self.rank}")
+            if str(plan.mesh) != str(self.mesh) or plan.rank != self.rank:
+                raise SystemExit(f"plan file is for mesh {plan.mesh} rank {plan.rank}, not {self.mesh} rank {self.rank}")
+            return plan
+        plan = self._build_plan(args)
+        if getattr(args, "save_plan", None):
+            plan.save(f"{args.save_plan}.rank{self.rank}")
+        return plan
+
+    def _build_plan(self, args):
         if args.gen:
             m = generate.from_spec(args.gen, seed=args.seed)
             _, plan = build_my_plan(m, self.mesh, self.rank, seed=args.seed, policy=args.policy)

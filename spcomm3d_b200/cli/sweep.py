@@ -6,9 +6,10 @@
 Prints one JSON line per (mesh, variant, k, kernel): device-timed ms/iter (max
 over ranks), GFLOP/s, the plan's communication volume (max and sum over ranks,
 bytes actually needed = the sparsity-aware minimum), and for the fused
-variant the in-kernel pull time with the NVLink rate it implies and the
-achieved fraction of the roofline max(NVLink bytes / link bandwidth, local
-gather bytes / HBM bandwidth).  This is the programme that fills the
+variant the in-kernel pull time and the achieved fraction of the roofline
+max(FLOPs / peak, bytes needed over NVLink / link bandwidth); the no-reuse
+gather model (one dense row per nonzero at the device-memory copy rate) is
+printed beside it for orientation.  This is the programme that fills the
 comparison grid of meshes the reference runs by hand with different `-c`
 values (miniapp/bench_spmm.cpp:137-143).
 """
@@ -107,11 +108,7 @@ def main(argv=None):
                         rec["pull_ms"] = round(float(mx[3]), 4)
                         rec["main_ms"] = round(float(mx[4]), 4)
                     rt.say(json.dumps(rec))
-                    if op.variant == "fused":
-                        op._fused.check()
-                        if hasattr(op._fused, "release"):  # multicast binding: dropped by all ranks together
-                            rt.barrier()
-                            op._fused.release()
+                    op.close()   # collective: status check, multicast binding dropped by all ranks together
                     del op
     rt.finish()
 

@@ -54,7 +54,7 @@ class _Dist3DOp:
     kernel = "?"
 
     def __init__(self, plan: RankPlan, groups: MeshGroups | None, k: int, dtype=torch.float32,
-                 device="cpu", variant: str = "sparseNRB", emulated: bool = False):
+                 device="cpu", variant: str = "sparseNRB", emulated: bool = False, check_plan: bool = True):
         if variant not in VARIANTS:
             raise ValueError(f"variant must be one of {VARIANTS}")
         self.plan, self.groups, self.k, self.dtype, self.variant = plan, groups, k, dtype, variant
@@ -63,8 +63,16 @@ class _Dist3DOp:
         self.k_off, self.k_loc = split_k(k, self.mesh.Z, plan.coords[2])
         self.timer = PhaseTimer(self.device)
         self.last_times: dict = {}
+        # True: `run` does not raise on a status recorded by a fused kernel; `close` raises it, after all ranks
+        # have dropped what binds their memory to each other
+        self.defer_status = False
         if groups is None and self.mesh.size != 1 and not emulated:
             raise ValueError("a multi-rank mesh needs MeshGroups")
+        if groups is not None and check_plan and not plan.meta.get("consistent"):
+            # collective, once per plan: same mesh, matrix and seed on every rank before anything is launched
+            from ..parallel import health
+            health.check_consistent(plan, groups)
+            plan.meta["consistent"] = True
         if variant == "fused" and self.device.type != "cuda":
             raise ValueError("the fused variant runs on GPUs only")
         self.rowptr = torch.from_numpy(plan.rowptr).to(self.device)
@@ -110,7 +118,7 @@ class _Dist3DOp:
     def _finish(self):
         if not self.timer.enabled:
             return None
-        if self.variant == "fused":
+        if self.variant == "fused" and not self.defer_status:
             self._fused.check()
         self.last_times = self.timer.collect()
         t = self.last_times
@@ -126,6 +134,30 @@ class _Dist3DOp:
         finally:
             self.timer.enabled = True
 
+    def close(self):
+        """Collective shutdown: every rank calls it, with none of its kernels in flight.  Synchronises, meets
+        the other ranks, drops what binds this rank's memory to its peers (the NVLink multicast binding of the
+        in-switch Z reduction), and meets them again, so that no rank leaves while its memory is still bound.
+        A status recorded by a fused kernel is raised only after the release."""
+        f = getattr(self, "_fused", None)
+        if f is None:
+            return
+        import torch.distributed as dist
+        err = None
+        try:
+            f.check()
+        except Exception as e:  # report after the collective release
+            err = e
+        multi = self.groups is not None and dist.is_initialized()
+        if multi:
+            dist.barrier()
+        if hasattr(f, "release"):
+            f.release()
+        if multi:
+            dist.barrier()
+        if err is not None:
+            raise err
+
     def alg_name(self, phase: str) -> str:
         return f"{ALG_NAMES[self.variant]} {self.kernel} {phase}"
 
@@ -138,7 +170,8 @@ class DistSDDMM(_Dist3DOp):
             variant = "fused"
         if variant == "fused-multimem":  # Z reduction of the partial values inside the NVSwitch
             variant, kw = "fused", {**kw, "zreduce": "multimem"}
-        super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
+        super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None,
+                         check_plan=kw.get("check_plan", True))
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSDDMM
@@ -221,7 +254,8 @@ class DistSpMM(_Dist3DOp):
             variant, kw = "fused", {**kw, "reduce": "atomic"}
         if variant == "fused-multimem":  # only SDDMM has a Z reduction
             variant = "fused"
-        super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None)
+        super().__init__(plan, groups, k, dtype, device, variant, emulated=kw.get("heap") is not None,
+                         check_plan=kw.get("check_plan", True))
         p = plan
         if variant == "fused":
             from ..ops.fused import FusedSpMM

@@ -106,6 +106,59 @@ class SddmmSpmmStep:
             self._sums[0], self._sums[1] = c.double().sum(), y.double().sum()
         return self._sums.cpu().tolist()
 
+    # ---- health, timing breakdown, shutdown --------------------------------
+    def check(self):
+        """Synchronises and raises `FusedStatusError` if a fused kernel of either op recorded a bad index
+        or a wait that ran out since the last check (the asynchronous run path does not look)."""
+        for op in (self.sddmm, self.spmm):
+            f = getattr(op, "_fused", None)
+            if f is not None:
+                f.check()
+
+    def phase_ms(self):
+        """In-kernel time stamps of the last fused launches: {"sddmm": {"pull", "main", "total"}, "spmm": ...}
+        in milliseconds, or None for the library variants."""
+        if getattr(self.sddmm, "_fused", None) is None:
+            return None
+        return {"sddmm": self.sddmm._fused.phase_ms(), "spmm": self.spmm._fused.phase_ms()}
+
+    def local_kernel_ms(self, iters: int = 5):
+        """(sddmm_ms, spmm_ms) of the plain local kernels on this rank's block with every dense row already
+        in local memory: what the distributed ops would cost if communication were free."""
+        from ..ops import local
+        sd, sp, p = self.sddmm, self.spmm, self.plan
+        dev, dt, kl = self.device, sd.dtype, sd.k_loc
+        f = getattr(sd, "_fused", None)
+        A = f._A_full if f is not None else sd.A_loc
+        Y = torch.empty(p.row.n_local, kl, dtype=dt, device=dev)
+        sched = sp.sched
+        if sched is None and dev.type == "cuda":
+            sched = sp._fused.sched if getattr(sp, "_fused", None) is not None else None
+        out = []
+        for fn in (lambda: local.sddmm(sd.rowidx, sd.colidx, sd.vals, A, sd.B_loc, out=sd.partial),
+                   lambda: local.spmm(sp.rowptr, sp.rowidx, sp.colidx, sp.vals, sp.X_loc, Y, 0.0, sched)):
+            fn()
+            if dev.type == "cuda":
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(iters):
+                    fn()
+                b.record()
+                torch.cuda.synchronize(dev)
+                out.append(a.elapsed_time(b) / iters)
+            else:
+                import time
+                t0 = time.perf_counter()
+                for _ in range(iters):
+                    fn()
+                out.append((time.perf_counter() - t0) * 1e3 / iters)
+        return tuple(out)
+
+    def close(self):
+        """Collective shutdown of both ops (see `_Dist3DOp.close`)."""
+        self.sddmm.close()
+        self.spmm.close()
+
     def comm_volume_bytes(self):
         """[sddmm expand, sddmm z-reduce, spmm expand, spmm reduce] bytes this
         rank receives per step according to the plan."""

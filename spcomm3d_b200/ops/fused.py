@@ -23,6 +23,8 @@ from ..utils import native
 from . import cuda_ops
 
 MAX_RANKS = 64
+MAX_WAVES = 32   # pull waves a kernel can track (csrc/kernels/fused_ops.cu)
+PULL_ROWS = 64   # dense rows per pull tile
 F_KINDS = 3
 PH_START, PH_MAIN, PH_FINISH = 1, 2, 4
 PH_ALL = 7
@@ -45,7 +47,8 @@ class _SddmmArgs(C.Structure):
                 ("n_recv_b", C.c_int), ("b_src", P), ("nvec", C.c_int), ("Z", C.c_int), ("my_z", C.c_int),
                 ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P),
                 ("part", P), ("direct_push", C.c_int), ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int),
-                ("n_recv_a", C.c_int), ("a_src", P), ("A_stage", P), ("mc_part", P), ("part_stride", C.c_longlong)]
+                ("n_recv_a", C.c_int), ("a_src", P), ("A_stage", P), ("mc_part", P), ("part_stride", C.c_longlong),
+                ("pull_order", P), ("n_waves", C.c_int), ("tiles_per_wave", C.c_int), ("wave_nnz", P)]
 
 
 class _SpmmLong(C.Structure):
@@ -116,7 +119,7 @@ class _FusedBase:
         self.epoch = 0
         self.timeout_ns = int(timeout_s * 1e9)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.ctrl = torch.zeros(16, dtype=torch.int32, device=self.device)
+        self.ctrl = torch.zeros(int(native.cuda().sp3_fused_ctrl_words()), dtype=torch.int32, device=self.device)
         self.pad = heap.view("pad", torch.int32, (F_KINDS * MAX_RANKS,))
         self.peer_pad = self._dev_i64([heap.addr("pad", r) for r in range(heap.world)])
         self._keep = []
@@ -212,12 +215,12 @@ class FusedSDDMM(_FusedBase):
         p, h, k = self.plan, self.heap, self.k_loc
         Z, z = p.mesh.Z, p.coords[2]
         # A block: my owned rows (peers read them in place) followed by room for staged copies of the remote
-        # rows I need.  Default: every remote A row is read straight from its owner when a work unit first
-        # needs it (measured equal or faster on 2 GPUs: 0.458 vs 0.475 ms, R-MAT-20, 1x2x1); stage_a pulls
-        # them in bulk like the B rows instead.
+        # rows I need.  stage_a (default): the needed remote A rows are pulled in bulk like the B rows, many
+        # loads in flight per warp; the compute loop then reads local memory only.  stage_a=False reads every
+        # remote A row straight from its owner when a work unit first needs it: no staging traffic, but the
+        # unit stalls for one NVLink round trip per row change, which costs more than the copy on real links.
         if stage_a is None:
-            stage_a = os.environ.get("SP3_FUSED_STAGE_A", "0") == "1"
-        self.stage_a = bool(stage_a)
+            stage_a = os.environ.get("SP3_FUSED_STAGE_A", "1") == "1"
         self._A_full = h.view("A", torch.float32, (p.row.n_local, k))
         self.A_loc = self._A_full[:p.row.n_owned]
         self.B_loc = h.view("B", torch.float32, (p.col.n_local, k))
@@ -255,20 +258,17 @@ class FusedSDDMM(_FusedBase):
         n_recv_a = p.row.n_recv if self.stage_a else 0
         a.n_recv_a, a.a_src = n_recv_a, self.a_src.data_ptr()
         a.A_stage = self._A_full.data_ptr() + p.row.n_owned * self.row_bytes
+        a.pull_order, a.n_waves, a.tiles_per_wave, a.wave_nnz = None, 0, 0, None
         if overlap and (p.col.n_recv + n_recv_a) > 0 and p.nnz > 0:
-            needs_pull = p.colidx >= p.col.n_owned
-            if self.stage_a:
-                needs_pull = needs_pull | (p.rowidx >= p.row.n_owned)
-            order = np.argsort(needs_pull, kind="stable")
-            nnz_free = int(p.nnz - needs_pull.sum())
+            order, wave_nnz = self._plan_waves(p, n_recv_a)
             self._perm = (self._dev_i32(p.rowidx[order]), self._dev_i32(p.colidx[order]),
                           torch.from_numpy(p.vals[order]).to(device=self.device, dtype=torch.float32),
                           self._dev_i32(order))
             a.rowidx, a.colidx, a.sval, a.orig = (t.data_ptr() for t in self._perm)
-            a.nnz_free = nnz_free
-            nnz_per_ticket = 4 * 64  # a few units of 32..64 nonzeros (the kernel sizes tickets itself)
-            n_pull = -(-p.col.n_recv // 64) + -(-n_recv_a // 64)
-            a.work_per_pull = max(1, min(64, (nnz_free // nnz_per_ticket) // max(1, n_pull)))
+            a.nnz_free = int(wave_nnz[0])
+            a.work_per_pull = 1
+            a.wave_nnz = self._wave_nnz.data_ptr()
+            a.pull_order = self._pull_order.data_ptr()
         else:
             a.rowidx, a.colidx, a.sval = op.rowidx.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
             a.orig, a.nnz_free, a.work_per_pull = None, 0, 1 << 30
@@ -303,6 +303,44 @@ class FusedSDDMM(_FusedBase):
         if Z > 1 and self.zreduce == "multimem":
             direct_push = 3   # nothing is pushed: the slice owners reduce through the multicast address
         a.direct_push = self.push_mode = direct_push
+
+    def _plan_waves(self, p, n_recv_a: int, target_waves: int | None = None):
+        """Order of the pull tiles, their grouping into waves, and the order of the nonzeros by the wave that
+        completes them.  Returns (order, wave_nnz): `order` lists the nonzeros class by class (class 0: both
+        dense rows owned; class c: the later of its two rows arrives with wave c - 1), each class in the
+        plan's row-sorted order; wave_nnz[c] = nonzeros of classes 0..c.
+
+        Tiles of A rows and tiles of B rows are interleaved in proportion, so that both operands arrive at the
+        same relative pace and a nonzero whose two rows come early in their receive lists is ready early."""
+        if target_waves is None:
+            target_waves = int(os.environ.get("SP3_FUSED_WAVES", "16"))
+        target_waves = max(1, min(MAX_WAVES, target_waves))
+        n_a, n_b = -(-n_recv_a // PULL_ROWS), -(-p.col.n_recv // PULL_ROWS)
+        n_pull = n_a + n_b
+        key = np.concatenate([(np.arange(n_a) + 0.5) / max(n_a, 1), (np.arange(n_b) + 0.5) / max(n_b, 1)])
+        code = np.concatenate([np.arange(n_a, dtype=np.int64) | (1 << 30), np.arange(n_b, dtype=np.int64)])
+        seq = np.argsort(key, kind="stable")
+        pull_order = code[seq]
+        tpw = -(-n_pull // target_waves)
+        n_waves = -(-n_pull // tpw)
+        ticket_of = np.empty(n_pull, np.int64)     # ticket number of tile i (A tiles first, then B tiles)
+        ticket_of[seq] = np.arange(n_pull)
+        wave_a, wave_b = ticket_of[:n_a] // tpw, ticket_of[n_a:] // tpw
+        cls = np.zeros(p.nnz, np.int8)
+        rem_b = p.colidx >= p.col.n_owned
+        cls[rem_b] = wave_b[(p.colidx[rem_b] - p.col.n_owned) // PULL_ROWS] + 1
+        if n_recv_a:
+            rem_a = p.rowidx >= p.row.n_owned
+            ca = np.zeros(p.nnz, np.int8)
+            ca[rem_a] = wave_a[(p.rowidx[rem_a] - p.row.n_owned) // PULL_ROWS] + 1
+            np.maximum(cls, ca, out=cls)
+        order = np.argsort(cls, kind="stable")
+        wave_nnz = np.cumsum(np.bincount(cls, minlength=n_waves + 1)).astype(np.int64)
+        self._pull_order = self._dev_i32(pull_order)
+        self._wave_nnz = self._dev_i64(wave_nnz)
+        self.args.n_waves, self.args.tiles_per_wave = int(n_waves), int(tpw)
+        self.wave_nnz = wave_nnz
+        return order, wave_nnz
 
     def _multicast_part(self, op, nnz: int):
         """Partial-value buffer [2][nnz rounded up to 4] in torch symmetric memory, bound to a multicast object

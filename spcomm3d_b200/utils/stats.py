@@ -79,35 +79,45 @@ def report_iteration(op, groups=None, rank: int = 0, out=print):
     return aggs
 
 
-def measured_peaks() -> dict:
-    """{"hbm_gbs", "nvlink_gbs", "source"}: the copy bandwidth measured on this pool's GPUs if a
-    MEASURED_PEAKS.json lies at the repository root (key `hbm_gbs`), else 6549.8 GB/s from an earlier
-    measurement; 770 GB/s per direction for a peer copy over NVLink (measured on the same class of box)."""
-    from pathlib import Path
-    out = {"hbm_gbs": 6549.8, "nvlink_gbs": 770.0, "source": "built-in (earlier measurement)"}
-    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
-    try:
-        d = json.loads(f.read_text())
-        if float(d.get("hbm_gbs", 0)) > 0:
-            out["hbm_gbs"], out["source"] = float(d["hbm_gbs"]), f.name
-    except (OSError, ValueError):
-        pass
+def measured_peaks(path: str | None = None) -> dict:
+    """{"hbm_gbs", "nvlink_gbs", "source"}: denominators of the rooflines.  Defaults: 6549.8 GB/s for a
+    device-memory copy and 770 GB/s per direction for a peer copy over NVLink (both measured on B200 boxes).
+    A JSON file with a key `hbm_gbs` overrides the first; it is looked for at `path`, else at the path in the
+    environment variable SP3_PEAKS_FILE; SP3_HBM_GBS / SP3_NVLINK_GBS override single figures."""
+    import os
+    out = {"hbm_gbs": 6549.8, "nvlink_gbs": 770.0, "source": "built-in"}
+    path = path or os.environ.get("SP3_PEAKS_FILE")
+    if path:
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            if float(d.get("hbm_gbs", 0)) > 0:
+                out["hbm_gbs"], out["source"] = float(d["hbm_gbs"]), os.path.basename(path)
+        except (OSError, ValueError):
+            pass
+    for key, env in (("hbm_gbs", "SP3_HBM_GBS"), ("nvlink_gbs", "SP3_NVLINK_GBS")):
+        if os.environ.get(env):
+            out[key], out["source"] = float(os.environ[env]), "environment"
     return out
 
 
 def roofline(flops: float, nvlink_bytes_per_rank: float, hbm_bytes_per_rank: float, ms: float,
              peak_tflops: float = 70.0, nvlink_gbs: float = 770.0, hbm_gbs: float = 6549.8) -> dict:
-    """Time floor of a fused op = the slowest of its FLOPs at peak, its NVLink
-    bytes at link bandwidth and its local HBM bytes at copy bandwidth; returns
-    the floor and achieved fraction.  `peak_tflops` is the fp32 FMA peak that
-    applies to these kernels (not the tensor-core peak)."""
+    """Roofline of a fused op: the slower of its FLOPs at peak and the bytes it must move over NVLink at link
+    bandwidth (`floor_ms`, `fraction` = floor / measured time, `bound`).  `peak_tflops` is the fp32 FMA peak
+    that applies to these kernels (not the tensor-core peak).
+
+    A second, informative figure: `gather_model_ms` = the dense rows the local kernel fetches (one row per
+    nonzero, no reuse) at the device-memory copy rate, with `gather_model_fraction`.  It is a model of the
+    local gather without cache reuse, not a bound: a kernel whose rows are served by the L2 beats it."""
     t_flop = flops / (peak_tflops * 1e12) * 1e3
     t_link = nvlink_bytes_per_rank / (nvlink_gbs * 1e9) * 1e3
     t_hbm = hbm_bytes_per_rank / (hbm_gbs * 1e9) * 1e3
-    floor = max(t_flop, t_link, t_hbm)
-    return {"floor_ms": floor, "flop_ms": t_flop, "nvlink_ms": t_link, "hbm_ms": t_hbm,
+    floor = max(t_flop, t_link)
+    return {"floor_ms": floor, "flop_ms": t_flop, "nvlink_ms": t_link,
             "fraction": floor / ms if ms > 0 else 0.0,
-            "bound": max((t_flop, "flops"), (t_link, "nvlink"), (t_hbm, "hbm"))[1]}
+            "bound": "flops" if t_flop >= t_link else "nvlink",
+            "gather_model_ms": t_hbm, "gather_model_fraction": t_hbm / ms if ms > 0 else 0.0}
 
 
 def json_record(op, kernel: str, ms: float, extra: dict | None = None) -> str:

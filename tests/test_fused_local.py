@@ -27,7 +27,7 @@ MESHES = ["2x2x2", "4x2x1", "1x1x8", "2x1x2", "1x2x1", "3x2x1"]
 
 # (pull/compute overlap, push mode of the Z partials: 1 direct, 0 staged + bulk, 2 staged + per-ticket, staged A rows)
 @pytest.mark.parametrize("overlap,push,stage_a", [(True, 1, False), (False, 0, True), (False, 2, False),
-                                                  (True, None, False)])
+                                                  (True, None, False), (True, 0, True), (True, None, None)])
 @pytest.mark.parametrize("meshstr", MESHES)
 @pytest.mark.parametrize("gen,k", [("uniform:600:500:7", 64), ("zipf:700:900:1.6:600", 32)])
 def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap, push, stage_a):
@@ -118,6 +118,43 @@ def test_fused_spmm_all_ranks_one_gpu(meshstr, gen, k, reduce, red_v4):
             assert torch.equal(op.Y_owned, y0)
         elif y0.numel():  # atomic adds: the order of the additions may differ between runs
             assert (op.Y_owned - y0).abs().max() <= 1e-5 * max(1.0, float(y0.abs().max()))
+
+
+def test_atomic_spmm_start_and_main_in_one_launch():
+    """Atomic mode with START and MAIN in the same launch (what real ranks run): the rows that receive
+    contributions are cleared by START warps with plain stores, and no warp -- of this rank either -- may add
+    into them before all START warps are done.  Rank 1's START runs first, alone, so that rank 0 can run START
+    and MAIN in one launch without waiting for a later launch; no dense row is pulled on a 1x2x1 mesh, so
+    nothing else delays rank 0's MAIN warps."""
+    from spcomm3d_b200.models.dist_ops import DistSpMM
+    from spcomm3d_b200.ops import oracle
+    from spcomm3d_b200.ops.fused import FusedSpMM, PH_FINISH, PH_MAIN, PH_START
+    from spcomm3d_b200.parallel.symm import LocalFabric
+    from spcomm3d_b200.utils import generate
+    k = 64
+    mesh, m, plans, A, B = _setup("1x2x1", "zipf:4000:3000:1.5:900", k)
+    fabric = LocalFabric(mesh.size)
+    heaps = fabric.heaps([FusedSpMM.region_sizes(plans[r], k, "atomic") for r in range(mesh.size)])
+    ops = [DistSpMM(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0,
+                    reduce="atomic") for r in range(mesh.size)]
+    assert all(op._fused.args.n_recv_x == 0 and op._fused.args.n_crows > 0 for op in ops)
+    full = oracle.spmm_ref(m, B)
+    for op in ops:
+        op.fill_owned(op.X_owned, op.plan.col.owned_gids, seed=5, stream=2)
+    for epoch in range(25):
+        for op in ops:
+            op.Y_owned.fill_(float("nan"))
+        f0, f1 = ops[0]._fused, ops[1]._fused
+        f1.launch(ops[1].Y_owned, 0.0, phases=PH_START, new_epoch=True)
+        f0.launch(ops[0].Y_owned, 0.0, phases=PH_START | PH_MAIN, new_epoch=True)
+        f1.launch(ops[1].Y_owned, 0.0, phases=PH_MAIN, new_epoch=False)
+        f0.launch(ops[0].Y_owned, 0.0, phases=PH_FINISH, new_epoch=False)
+        f1.launch(ops[1].Y_owned, 0.0, phases=PH_FINISH, new_epoch=False)
+        for op in ops:
+            op._fused.check()
+            ref = full[op.plan.row.owned_gids]
+            err = (op.Y_owned.cpu().double() - ref).abs().max()
+            assert err <= 2e-5 * max(1.0, ref.abs().max()) * 8, (epoch, op.plan.rank, float(err))
 
 
 def test_wait_runs_out_without_hanging():

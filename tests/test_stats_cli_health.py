@@ -29,6 +29,11 @@ def test_stats_line_roundtrip_and_reference_layout():
 def test_roofline_picks_the_slowest_resource():
     r = stats.roofline(flops=2e9, nvlink_bytes_per_rank=0.5e9, hbm_bytes_per_rank=1e9, ms=1.0)
     assert r["bound"] == "nvlink" and abs(r["nvlink_ms"] - 0.5e9 / 770e9 * 1e3) < 1e-9 and 0 < r["fraction"] < 1
+    # the no-reuse gather model is reported beside the roofline, never as its floor
+    big = stats.roofline(flops=2e9, nvlink_bytes_per_rank=0.5e9, hbm_bytes_per_rank=1e12, ms=1.0)
+    assert big["floor_ms"] == r["floor_ms"] and big["gather_model_ms"] > big["floor_ms"]
+    r = stats.roofline(flops=2e15, nvlink_bytes_per_rank=0.0, hbm_bytes_per_rank=0.0, ms=100.0)
+    assert r["bound"] == "flops"
 
 
 def _torchrun(n, module, *args):
@@ -72,7 +77,7 @@ def test_sweep_cli_reports_every_mesh_and_variant():
         for kern in ("sddmm", "spmm"):
             assert by[(mesh, "sparseNRB", kern)]["comm_bytes_total"] <= by[(mesh, "dense", kern)]["comm_bytes_total"]
     for r in recs:
-        assert r["ms"] > 0 and r["roofline"]["floor_ms"] >= 0 and r["roofline"]["bound"] in ("nvlink", "hbm", "flops")
+        assert r["ms"] > 0 and r["roofline"]["floor_ms"] >= 0 and r["roofline"]["bound"] in ("nvlink", "flops")
 
 
 def test_checksum_tools_agree(tmp_path):
