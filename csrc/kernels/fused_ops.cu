@@ -41,6 +41,7 @@
 // lock step (each phase of every rank before the next phase) without any
 // kernel ever waiting on a later launch.
 #include "sp3_kernels.cuh"
+#include "sp3_async.cuh"
 
 namespace sp3 {
 
@@ -180,6 +181,73 @@ __device__ __forceinline__ void pull_rows(int r0, int r1, const float4* const* _
     }
 }
 
+// The same copy with the asynchronous copy unit (bulk mode): one warp per block keeps a ring of BULK_STAGES
+// shared-memory stages; every dense row travels as one `cp.async.bulk` load from its owner's memory (a peer
+// mapping or local) into a stage, completing on the stage's mbarrier, and every filled stage leaves as one bulk
+// store into the local block (the rows of a tile are consecutive there).  Nothing passes through registers and
+// the warp never stalls on a load, so a few warps keep NVLink busy while all the others compute.
+constexpr int BULK_STAGES = 3;
+constexpr unsigned BULK_STAGE_BYTES = 8192;
+constexpr unsigned BULK_SMEM_BYTES = BULK_STAGES * BULK_STAGE_BYTES + 64;
+
+struct BulkRing {
+    unsigned ring, bars;    // shared-memory addresses of the stages and of their mbarriers
+    unsigned long long g;   // chunks this warp has issued so far: stage g % BULK_STAGES, phase parity (g / BULK_STAGES) & 1
+};
+
+// Copies rows [r0, r1) of a receive list into dst (row r lands at dst + r * nvec vectors; the local block has
+// no padding between rows).  All lanes of one warp call it.  Returns false when a load did not arrive in time
+// (status recorded, abort raised); the copies still in flight are then given the same time again before the
+// warp moves on, because their destination is this block's shared memory.
+__device__ __forceinline__ bool bulk_pull_tile(BulkRing& br, const FusedComm& c, int r0, int r1,
+                                               const float4* const* __restrict__ src, float4* __restrict__ dst,
+                                               int nvec, int lane) {
+    const unsigned row_bytes = (unsigned)nvec * 16u;
+    int rps = (int)(BULK_STAGE_BYTES / row_bytes);   // rows per stage
+    rps = rps > PULL_ROWS ? PULL_ROWS : (rps < 1 ? 1 : rps);
+    const int n = r1 - r0, nch = (n + rps - 1) / rps;
+    bool ok = true;
+    for (int ch = 0; ch < nch + BULK_STAGES - 1; ++ch) {
+        if (ch < nch && ok) {
+            const unsigned st = (unsigned)((br.g + ch) % BULK_STAGES);
+            // the store that read this stage last was issued one step ago at the latest: wait until it has let go
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+            const int c0 = ch * rps, cn = n - c0 < rps ? n - c0 : rps;
+            if (lane == 0) mbar_expect_tx(br.bars + 8u * st, (unsigned)cn * row_bytes);
+            __syncwarp();
+            for (int i = lane; i < cn; i += 32)
+                bulk_load(br.ring + st * BULK_STAGE_BYTES + (unsigned)i * row_bytes, ldg_ptr(src + r0 + c0 + i),
+                          row_bytes, br.bars + 8u * st);
+        }
+        const int pc = ch - (BULK_STAGES - 1);
+        if (pc >= 0 && pc < nch) {
+            const unsigned long long gi = br.g + pc;
+            const unsigned st = (unsigned)(gi % BULK_STAGES), par = (unsigned)((gi / BULK_STAGES) & 1);
+            const bool arrived = mbar_wait_ns(br.bars + 8u * st, par, c.timeout_ns);
+            if (!arrived && ok) {
+                ok = false;
+                report(c.status, ST_WAIT_TIMEOUT, W_PULLS, r0 + pc * rps, (int)st);
+                atomicExch(c.ctrl + C_ABORT, 1);
+            }
+            if (ok) {
+                const int c0 = pc * rps, cn = n - c0 < rps ? n - c0 : rps;
+                if (lane == 0) {
+                    bulk_store(dst + (long long)(r0 + c0) * nvec, br.ring + st * BULK_STAGE_BYTES, (unsigned)cn * row_bytes);
+                    bulk_commit();
+                }
+            }
+        }
+    }
+    br.g += nch;
+    if (lane == 0) {
+        bulk_wait<0>();        // the stores of this tile are complete ...
+        fence_async_proxy();   // ... and ordered before the ordinary accesses that publish the tile
+    }
+    __syncwarp();
+    return ok;
+}
+
 // Every warp calls this after its MAIN work; the last one to arrive publishes
 // DONE and PART for this rank.
 __device__ __forceinline__ void main_epilogue(const FusedComm& c, int lane, int nwarps) {
@@ -271,6 +339,7 @@ struct FusedSddmmArgs {
     const int* pull_order;
     int n_waves, tiles_per_wave;
     const long long* wave_nnz;
+    int bulk_pull;                // 1: the first warp of every block pulls with bulk copies (see bulk_pull_tile)
 };
 
 // Sum over all devices of a multicast object, added in the NVSwitch (NVLS); `p` is a multicast address.
@@ -323,7 +392,18 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
     __shared__ unsigned long long a_bases[MAX_RANKS];
+    extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: BULK_SMEM_BYTES, else nothing
     if (threadIdx.x < MAX_RANKS) a_bases[threadIdx.x] = threadIdx.x < a.world ? a.a_bases[threadIdx.x] : 0ull;
+    const bool bulk = a.bulk_pull != 0;
+    BulkRing br{0u, 0u, 0ull};
+    if (bulk) {
+        br.ring = smem_u32(dyn_smem);
+        br.bars = br.ring + BULK_STAGES * BULK_STAGE_BYTES;
+        if (threadIdx.x == 0) {
+            for (int st = 0; st < BULK_STAGES; ++st) mbar_init(br.bars + 8u * st, 1);
+            mbar_init_fence();
+        }
+    }
     __syncthreads();
     if (c.phases & PH_START) start_phase(c);
     if (c.phases & PH_MAIN) {
@@ -344,7 +424,11 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
                                  a.zbase, a.zrem, a.zwidth};
         float4* Bv = reinterpret_cast<float4*>(a.B_loc);
         const long long ldb_v = a.ldb / 4;
-        bool pulls_left = n_pull > 0;
+        const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+        // pullers: in bulk mode the first warp of every block and nobody else; otherwise one warp in four,
+        // helped by any warp whose own units are not ready yet
+        const bool is_puller = bulk ? threadIdx.x < 32 : (gwarp & 3) == 0;
+        bool pulls_left = n_pull > 0 && (!bulk || is_puller);
         const long long n_free_units = a.nnz_free / per_unit;  // units that touch no pulled row
         const int n_waves = n_pull > 0 ? (a.n_waves > 0 ? a.n_waves : 1) : 0;
         const int tpw = a.n_waves > 0 ? a.tiles_per_wave : (n_pull > 0 ? n_pull : 1);
@@ -353,15 +437,14 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
             if (t >= n_pull) return false;
             const int code = a.pull_order ? __ldg(a.pull_order + t) : (t < n_pull_a ? (t | (1 << 30)) : t - n_pull_a);
             const int tile = code & ((1 << 30) - 1);
-            if (code >> 30) {
-                const int r0 = tile * PULL_ROWS;
-                const int r1 = r0 + PULL_ROWS < a.n_recv_a ? r0 + PULL_ROWS : a.n_recv_a;
-                pull_rows(r0, r1, a.a_src, reinterpret_cast<float4*>(a.A_stage), ldb_v, a.nvec, lane);
-            } else {
-                const int r0 = tile * PULL_ROWS;
-                const int r1 = r0 + PULL_ROWS < a.n_recv_b ? r0 + PULL_ROWS : a.n_recv_b;
-                pull_rows(r0, r1, a.b_src, Bv + (long long)a.n_owned_b * ldb_v, ldb_v, a.nvec, lane);
-            }
+            const bool side_a = (code >> 30) != 0;
+            const int n_side = side_a ? a.n_recv_a : a.n_recv_b;
+            const float4* const* src = side_a ? a.a_src : a.b_src;
+            float4* dst = side_a ? reinterpret_cast<float4*>(a.A_stage) : Bv + (long long)a.n_owned_b * ldb_v;
+            const int r0 = tile * PULL_ROWS;
+            const int r1 = r0 + PULL_ROWS < n_side ? r0 + PULL_ROWS : n_side;
+            if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, src, dst, a.nvec, lane)) return false; }
+            else pull_rows(r0, r1, src, dst, ldb_v, a.nvec, lane);
             __threadfence();
             __syncwarp();
             if (lane == 0) {
@@ -391,13 +474,11 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
             }
             return true;
         };
-        // One warp in four is a puller: it serves pull tickets until none are left (a quarter of the warps,
-        // 4 KB of reads in flight each, is enough to fill NVLink) while the others start on the units that
-        // need no pulled row.
-        const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+        // The pullers serve pull tickets until none are left while the others start on the units that need no
+        // pulled row.
         (void)n_free_units;
-        if ((gwarp & 3) == 0)
-            while (ok && pulls_left) pulls_left = pull_one();
+        if (is_puller)
+            while (ok && pulls_left && !aborted(c)) pulls_left = pull_one();
         const int SDDMM_UNITS_PER_TICKET = per_ticket(n_units, nwarps, SDDMM_UNITS_PER_TICKET_MAX);
         while (ok) {
             const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
@@ -543,6 +624,7 @@ struct FusedSpmmArgs {
     int atomic;
     int red_v4;                   // 1: 16-byte vector atomics also for remote rows, 0: one 4-byte atomic per value
     const unsigned char* crow_flag;  // [n_owned_y] 1: row receives contributions from peers
+    int bulk_pull;                // 1: the first warp of every block pulls the X rows with bulk copies
 };
 
 // Rows I own go straight into the result (Y = beta*Y + my partial; the owners' FINISH phase then adds what
@@ -595,6 +677,18 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
     const int lane = threadIdx.x & 31;
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
+    extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: BULK_SMEM_BYTES, else nothing
+    const bool bulk = a.bulk_pull != 0;
+    BulkRing br{0u, 0u, 0ull};
+    if (bulk) {
+        br.ring = smem_u32(dyn_smem);
+        br.bars = br.ring + BULK_STAGES * BULK_STAGE_BYTES;
+        if (threadIdx.x == 0) {
+            for (int st = 0; st < BULK_STAGES; ++st) mbar_init(br.bars + 8u * st, 1);
+            mbar_init_fence();
+        }
+        __syncthreads();
+    }
     if ((c.phases & PH_START) && !ATOMIC) start_phase(c);
     if ((c.phases & PH_START) && ATOMIC) {
         // scale the rows that peers will add to, then tell readers and contributors that this rank is ready
@@ -637,12 +731,14 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
         const EmitOwnedOrPush emit{reinterpret_cast<float4*>(a.Y), a.ldy / 4, a.beta, a.n_owned_y, a.y_dst,
                                    parity ? a.parity_off_v : 0};
         bool pulled = n_pull == 0;
-        while (ok) {
+        // bulk mode: the first warp of every block pulls with the asynchronous copy unit; otherwise all warps pull
+        while (ok && (!bulk || threadIdx.x < 32) && !aborted(c)) {
             const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
             if (t >= n_pull) break;
             const int r0 = t * PULL_ROWS;
             const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
-            pull_rows(r0, r1, a.x_src, Xv + (long long)a.n_owned_x * ldx_v, ldx_v, a.nvec, lane);
+            if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, a.x_src, Xv + (long long)a.n_owned_x * ldx_v, a.nvec, lane)) break; }
+            else pull_rows(r0, r1, a.x_src, Xv + (long long)a.n_owned_x * ldx_v, ldx_v, a.nvec, lane);
             __threadfence();
             __syncwarp();
             if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
@@ -722,8 +818,9 @@ template <typename K, typename A>
 static int launch_resident(K kernel, const A& args, cudaStream_t st) {
     A copy = args;
     void* params[] = {&copy};
-    const unsigned blocks = persistent_blocks(kernel, 0);
-    return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(blocks), dim3(256), params, 0, st);
+    const size_t smem = args.bulk_pull ? BULK_SMEM_BYTES : 0;
+    const unsigned blocks = persistent_blocks(kernel, 0, 256, smem);
+    return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(blocks), dim3(256), params, smem, st);
 }
 
 SP3_API int sp3_fused_sddmm_f32(const void* args, void* stream) {

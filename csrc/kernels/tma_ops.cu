@@ -18,6 +18,7 @@
 // gather4 copy therefore delivers 4 x k elements (4 rows) to consecutive
 // shared memory.  The column coordinate of every copy is 0 (16-byte aligned).
 #include "sp3_kernels.cuh"
+#include "sp3_async.cuh"
 
 #include <cuda.h>
 
@@ -25,29 +26,6 @@ namespace sp3 {
 
 constexpr int TMA_MAX_STAGES = 8;
 constexpr int TMA_ROWS = 32;            // B rows per batch and warp (one per lane)
-constexpr unsigned TMA_WAIT_TRIES = 1u << 22;
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false after TMA_WAIT_TRIES unsuccessful probes.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned i = 0; i < TMA_WAIT_TRIES; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
 __device__ __forceinline__ void tma_gather4(unsigned dst, const CUtensorMap* map, unsigned bar, int col, int r0,
                                             int r1, int r2, int r3) {
     asm volatile(
@@ -77,8 +55,7 @@ sddmm_tma_kernel(const __grid_constant__ CUtensorMap mapB, long long nnz, const 
     const unsigned bar0 = smem_u32(bars + wid * stages);
     if (lane == 0)
         for (int s = 0; s < stages; ++s) mbar_init(bar0 + 8u * s, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_init_fence();
     __syncthreads();
 
     const V* Av = reinterpret_cast<const V*>(A);
@@ -198,8 +175,7 @@ spmm_tma_kernel(const __grid_constant__ CUtensorMap mapX, long long nnz, const i
     const unsigned bar0 = smem_u32(bars + wid * stages);
     if (lane == 0)
         for (int s = 0; s < stages; ++s) mbar_init(bar0 + 8u * s, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_init_fence();
     __syncthreads();
 
     const long long warp0 = (long long)blockIdx.x * nw + wid;

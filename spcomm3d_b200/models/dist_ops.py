@@ -176,7 +176,7 @@ class DistSDDMM(_Dist3DOp):
         if variant == "fused":
             from ..ops.fused import FusedSDDMM
             self._fused = FusedSDDMM(self, **{k_: v for k_, v in kw.items() if k_ in (
-                "heap", "fabric", "timeout_s", "overlap", "direct_push", "stage_a", "zreduce")})
+                "heap", "fabric", "timeout_s", "overlap", "direct_push", "stage_a", "zreduce", "bulk_pull")})
             self.A_loc, self.B_loc = self._fused.A_loc, self._fused.B_loc
         else:
             self.A_loc, self.B_loc = self._alloc_local(p.row), self._alloc_local(p.col)
@@ -260,7 +260,7 @@ class DistSpMM(_Dist3DOp):
         if variant == "fused":
             from ..ops.fused import FusedSpMM
             self._fused = FusedSpMM(self, **{k_: v for k_, v in kw.items()
-                                             if k_ in ("heap", "fabric", "timeout_s", "reduce", "red_v4")})
+                                             if k_ in ("heap", "fabric", "timeout_s", "reduce", "red_v4", "bulk_pull")})
             self.X_loc, self.Y_loc = self._fused.X_loc, self._fused.Y_loc
         else:
             self.X_loc, self.Y_loc = self._alloc_local(p.col), self._alloc_local(p.row)

@@ -48,7 +48,8 @@ class _SddmmArgs(C.Structure):
                 ("zbase", C.c_uint), ("zrem", C.c_uint), ("zwidth", C.c_longlong), ("zbuf", P), ("out", P),
                 ("part", P), ("direct_push", C.c_int), ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int),
                 ("n_recv_a", C.c_int), ("a_src", P), ("A_stage", P), ("mc_part", P), ("part_stride", C.c_longlong),
-                ("pull_order", P), ("n_waves", C.c_int), ("tiles_per_wave", C.c_int), ("wave_nnz", P)]
+                ("pull_order", P), ("n_waves", C.c_int), ("tiles_per_wave", C.c_int), ("wave_nnz", P),
+                ("bulk_pull", C.c_int)]
 
 
 class _SpmmLong(C.Structure):
@@ -62,7 +63,8 @@ class _SpmmArgs(C.Structure):
                 ("x_src", P), ("nvec", C.c_int), ("lg", _SpmmLong), ("n_owned_y", C.c_int), ("n_crows", C.c_int),
                 ("crows", P), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
                 ("ldy", C.c_longlong), ("beta", C.c_float), ("cptr", P), ("cslot", P), ("slots", P),
-                ("lds", C.c_longlong), ("atomic", C.c_int), ("red_v4", C.c_int), ("crow_flag", P)]
+                ("lds", C.c_longlong), ("atomic", C.c_int), ("red_v4", C.c_int), ("crow_flag", P),
+                ("bulk_pull", C.c_int)]
 
 
 _checked_layout = False
@@ -83,6 +85,15 @@ def _check_layout():
 
 class FusedStatusError(RuntimeError):
     pass
+
+
+def _bulk_default(bulk_pull):
+    """Pull mode of the fused kernels: True = remote rows travel as `cp.async.bulk` copies issued by one warp
+    per block (asynchronous copy unit, staged through shared memory); False = vector loads and stores by the
+    pulling warps.  Default from SP3_FUSED_BULK (1 unless set to 0)."""
+    if bulk_pull is None:
+        return os.environ.get("SP3_FUSED_BULK", "1") == "1"
+    return bool(bulk_pull)
 
 
 def _peer_ranks(plan, side: str):
@@ -205,8 +216,9 @@ class FusedSDDMM(_FusedBase):
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
                  overlap: bool = True, direct_push: bool | None = None, stage_a: bool | None = None,
-                 zreduce: str | None = None):
+                 zreduce: str | None = None, bulk_pull: bool | None = None):
         super().__init__(op, heap, fabric, timeout_s)
+        self.bulk_pull = _bulk_default(bulk_pull)
         if zreduce is None:
             zreduce = os.environ.get("SP3_FUSED_ZREDUCE", "push")
         if zreduce not in ("push", "multimem"):
@@ -221,6 +233,7 @@ class FusedSDDMM(_FusedBase):
         # unit stalls for one NVLink round trip per row change, which costs more than the copy on real links.
         if stage_a is None:
             stage_a = os.environ.get("SP3_FUSED_STAGE_A", "1") == "1"
+        self.stage_a = bool(stage_a)
         self._A_full = h.view("A", torch.float32, (p.row.n_local, k))
         self.A_loc = self._A_full[:p.row.n_owned]
         self.B_loc = h.view("B", torch.float32, (p.col.n_local, k))
@@ -303,6 +316,7 @@ class FusedSDDMM(_FusedBase):
         if Z > 1 and self.zreduce == "multimem":
             direct_push = 3   # nothing is pushed: the slice owners reduce through the multicast address
         a.direct_push = self.push_mode = direct_push
+        a.bulk_pull = int(self.bulk_pull)
 
     def _plan_waves(self, p, n_recv_a: int, target_waves: int | None = None):
         """Order of the pull tiles, their grouping into waves, and the order of the nonzeros by the wave that
@@ -397,7 +411,8 @@ class FusedSpMM(_FusedBase):
         return self.region_sizes(plan, k_loc, self.reduce)
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
-                 reduce: str | None = None, red_v4: bool | None = None):
+                 reduce: str | None = None, red_v4: bool | None = None, bulk_pull: bool | None = None):
+        self.bulk_pull = _bulk_default(bulk_pull)
         if reduce is None:
             reduce = os.environ.get("SP3_FUSED_SPMM_REDUCE", "slots")
         if reduce not in ("slots", "atomic"):
@@ -471,6 +486,7 @@ class FusedSpMM(_FusedBase):
         a.atomic, a.red_v4, a.crow_flag = int(self.atomic), int(bool(red_v4)), self.crow_flag.data_ptr()
         if self.atomic:
             a.parity_off_v = 0
+        a.bulk_pull = int(self.bulk_pull)
 
     def launch(self, Y: torch.Tensor, beta: float, phases=PH_ALL, new_epoch=True):
         if new_epoch:

@@ -25,12 +25,14 @@ def _setup(meshstr, gen, k, seed=3):
 MESHES = ["2x2x2", "4x2x1", "1x1x8", "2x1x2", "1x2x1", "3x2x1"]
 
 
-# (pull/compute overlap, push mode of the Z partials: 1 direct, 0 staged + bulk, 2 staged + per-ticket, staged A rows)
-@pytest.mark.parametrize("overlap,push,stage_a", [(True, 1, False), (False, 0, True), (False, 2, False),
-                                                  (True, None, False), (True, 0, True), (True, None, None)])
+# (pull/compute overlap in waves, push mode of the Z partials: 1 direct, 0 staged + one push at the end, 2 staged +
+#  per-ticket, staged A rows, pulls by bulk copies through shared memory instead of vector loads)
+@pytest.mark.parametrize("overlap,push,stage_a,bulk", [(True, 1, False, True), (False, 0, True, False),
+                                                       (False, 2, False, True), (True, None, False, False),
+                                                       (True, 0, True, True), (True, None, None, None)])
 @pytest.mark.parametrize("meshstr", MESHES)
 @pytest.mark.parametrize("gen,k", [("uniform:600:500:7", 64), ("zipf:700:900:1.6:600", 32)])
-def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap, push, stage_a):
+def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap, push, stage_a, bulk):
     from spcomm3d_b200.models.dist_ops import DistSDDMM
     from spcomm3d_b200.ops import oracle
     from spcomm3d_b200.ops.fused import FusedSDDMM, run_lockstep
@@ -42,7 +44,7 @@ def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap, push, stage_a):
     kl = [split_k(k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
     heaps = fabric.heaps([FusedSDDMM.region_sizes(plans[r], kl[r]) for r in range(mesh.size)])
     ops = [DistSDDMM(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0,
-                     overlap=overlap, direct_push=push, stage_a=stage_a)
+                     overlap=overlap, direct_push=push, stage_a=stage_a, bulk_pull=bulk)
            for r in range(mesh.size)]
     for epoch in range(2):
         for op in ops:
@@ -70,10 +72,11 @@ def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap, push, stage_a):
 
 # reduce: "slots" = per-source slots + ordered sum at the owner; "atomic" = adds into the owner's rows (16-byte
 # vector atomics, or one 4-byte atomic per value)
-@pytest.mark.parametrize("reduce,red_v4", [("slots", True), ("atomic", True), ("atomic", False)])
+@pytest.mark.parametrize("reduce,red_v4,bulk", [("slots", True, True), ("slots", True, False), ("atomic", True, None),
+                                                ("atomic", False, False)])
 @pytest.mark.parametrize("meshstr", MESHES)
 @pytest.mark.parametrize("gen,k", [("uniform:600:500:7", 64), ("zipf:700:900:1.6:600", 32)])
-def test_fused_spmm_all_ranks_one_gpu(meshstr, gen, k, reduce, red_v4):
+def test_fused_spmm_all_ranks_one_gpu(meshstr, gen, k, reduce, red_v4, bulk):
     from spcomm3d_b200.models.dist_ops import DistSpMM
     from spcomm3d_b200.ops import oracle
     from spcomm3d_b200.ops.fused import FusedSpMM, run_lockstep
@@ -85,7 +88,7 @@ def test_fused_spmm_all_ranks_one_gpu(meshstr, gen, k, reduce, red_v4):
     kl = [split_k(k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
     heaps = fabric.heaps([FusedSpMM.region_sizes(plans[r], kl[r], reduce) for r in range(mesh.size)])
     ops = [DistSpMM(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0,
-                    reduce=reduce, red_v4=red_v4)
+                    reduce=reduce, red_v4=red_v4, bulk_pull=bulk)
            for r in range(mesh.size)]
     results = []
     for epoch in range(3):
