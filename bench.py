@@ -280,7 +280,8 @@ def run_ours(args):
     # ---- correctness: a sample of every rank's results against fp64, and global checksums ----
     c, y = step.run_device()
     agree_healthy("in the verification step")
-    err_sd = verify.sample_sddmm_error(plan, c, args.k, args.seed, STREAM_A, STREAM_B)
+    err_sd = verify.sample_sddmm_error(plan, c, args.k, args.seed, STREAM_A, STREAM_B,
+                                       positions=step.sddmm.owned_positions())
     err_sp = verify.sample_spmm_error(plan, m, y, args.k, args.seed, STREAM_B)
     del m
     err_sd, err_sp = reduce([err_sd, err_sp], dist.ReduceOp.MAX)

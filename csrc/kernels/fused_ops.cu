@@ -293,7 +293,8 @@ struct FusedSddmmArgs {
     const int* rowidx;
     const int* colidx;
     const float* sval;
-    const int* a_refs;            // [rows of the local A layout] owner rank << 25 | row in the owner's block
+    const int* a_refs;            // [rows of the local A layout] owner rank << 25 | row in the owner's block;
+                                  // null when the needed remote rows are staged (every row is then local)
     const unsigned long long* a_bases;  // [world] address of every rank's A block as mapped here
     int world;
     float* B_loc;                 // local B block [owned | pulled]
@@ -415,7 +416,7 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         const int n_pull = n_pull_a + (a.n_recv_b + PULL_ROWS - 1) / PULL_ROWS;
         const long long per_unit = (long long)SLOTS * SDDMM_PER_SLOT;
         const long long n_units = (a.nnz + per_unit - 1) / per_unit;
-        const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull};
+        const RowsByPeerRef<float> arows{a.a_refs, a_bases, (unsigned long long)a.nvec * 16ull, c.me << PEER_REF_SHIFT};
         const int direct = a.Z > 1 && a.direct_push == 1;
         const bool self_push = a.Z > 1 && a.direct_push == 2 && a.orig == nullptr;
         const bool in_switch = a.Z > 1 && a.direct_push == 3;

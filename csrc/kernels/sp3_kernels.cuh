@@ -91,10 +91,11 @@ template <typename T> struct RowsByStride {
 constexpr int PEER_REF_SHIFT = 25;
 template <typename T> struct RowsByPeerRef {
     using V = typename Vec<T>::type;
-    const int* table;                  // [local rows] references
+    const int* table;                  // [local rows] references; null: every row is in this rank's own block
     const unsigned long long* bases;   // [ranks] block base addresses
     unsigned long long row_bytes;
-    __device__ __forceinline__ int ref(int row) const { return __ldg(table + row); }
+    int self_bits;                     // this rank << PEER_REF_SHIFT (used when table is null)
+    __device__ __forceinline__ int ref(int row) const { return table ? __ldg(table + row) : (self_bits | row); }
     __device__ __forceinline__ const V* resolve(int r) const {
         return reinterpret_cast<const V*>(bases[r >> PEER_REF_SHIFT] +
                                           (unsigned long long)(r & ((1 << PEER_REF_SHIFT) - 1)) * row_bytes);

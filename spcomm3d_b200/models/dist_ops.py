@@ -28,7 +28,10 @@ z-th slice of the k columns.  Variants:
                (ref "dense", src/dcomm_setup.cpp)
 
 SDDMM result: after the Z reduction fiber rank z holds the z-th contiguous
-slice of the block's values in the plan's CSR order.  SpMM result: owned rows
+slice of the block's values in the op's storage order: the plan's CSR order
+for the library variants; the fused variant stores values in the order it
+computes them and says which value is where (`value_order`,
+`owned_positions()`).  SpMM result: owned rows
 of Y; partial rows are summed at the owner in ascending peer order.  (The
 reference's sparse SpMM post step sends a stale buffer,
 src/distributed_comp.cpp:59; here it is defined by the math.)
@@ -227,6 +230,22 @@ class DistSDDMM(_Dist3DOp):
             c = c[self.owned_off:self.owned_off + self.owned_len]
         self._finish()
         return c
+
+    @property
+    def value_order(self):
+        """Storage order of the result values: None when they are in the plan's CSR order (library variants),
+        else an int64 array giving, for every stored value of the block, its position in the plan's CSR order
+        (the fused kernel stores its values in the order in which it computes them: nonzeros whose dense rows
+        are owned first, then the others by the pull wave that completes them)."""
+        f = getattr(self, "_fused", None)
+        return None if f is None else f.value_order
+
+    def owned_positions(self) -> np.ndarray:
+        """Positions, in the plan's CSR order, of the values `run` returns on this rank (after the Z reduction
+        fiber rank z holds the z-th contiguous slice of the block's values in storage order)."""
+        pos = np.arange(self.owned_off, self.owned_off + self.owned_len, dtype=np.int64)
+        order = self.value_order
+        return pos if order is None else np.asarray(order[pos], dtype=np.int64)
 
     def comm_stats(self):
         """{'PRE': ((send_msgs, send_vol), (recv_msgs, recv_vol)), 'POST': ...}

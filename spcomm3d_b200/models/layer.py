@@ -13,6 +13,7 @@
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -185,15 +186,24 @@ class GatLayer:
         dev = torch.device(device)
         self._mine = torch.zeros(self.width, dtype=dtype, device=dev)
         self._all = torch.zeros(Z, self.width, dtype=dtype, device=dev)
+        # the SpMM wants its values in CSR order; a fused SDDMM stores them in its own order
+        order = self.sddmm.value_order
+        self._pos = None if order is None else torch.from_numpy(np.ascontiguousarray(order)).to(dev)
 
     def run(self):
         c = self.sddmm.run()
         Z = self.plan.mesh.Z
         if Z == 1:
-            self.spmm.vals.copy_(c)
+            if self._pos is None:
+                self.spmm.vals.copy_(c)
+            else:
+                self.spmm.vals.index_copy_(0, self._pos, c)
         else:
             self._mine[:c.shape[0]].copy_(c)
             dist.all_gather_into_tensor(self._all.view(-1), self._mine, group=self.groups.fiber)
             for z, (o, l) in enumerate(self.slices):
-                self.spmm.vals[o:o + l].copy_(self._all[z, :l])
+                if self._pos is None:
+                    self.spmm.vals[o:o + l].copy_(self._all[z, :l])
+                else:
+                    self.spmm.vals.index_copy_(0, self._pos[o:o + l], self._all[z, :l])
         return self.spmm.run()

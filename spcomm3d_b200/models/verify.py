@@ -20,15 +20,17 @@ from ..utils import generate
 
 
 def sample_sddmm_error(plan, c_owned: torch.Tensor, k: int, seed: int, stream_a: int, stream_b: int,
-                       n_samples: int = 4096, rng_seed: int = 0) -> float:
+                       n_samples: int = 4096, rng_seed: int = 0, positions=None) -> float:
     """max |C - C_ref| / max |C_ref| over a sample of this rank's slice of C
-    (full-k dot products: the Z reduction has already summed the k slices)."""
+    (full-k dot products: the Z reduction has already summed the k slices).
+    `positions[i]` = position in the plan's CSR order of c_owned[i]
+    (`DistSDDMM.owned_positions()`; default: the rank's contiguous CSR slice)."""
     off, length = plan.owned_nnz_slice()
     if length == 0:
         return 0.0
     rng = np.random.default_rng(rng_seed + 7919 * plan.rank)
     idx = np.sort(rng.choice(length, size=min(n_samples, length), replace=False))
-    pos = off + idx
+    pos = off + idx if positions is None else np.asarray(positions)[idx]
     grow = plan.row.local_gids[plan.rowidx[pos]]
     gcol = plan.col.local_gids[plan.colidx[pos]]
     A = generate.fill_rows(grow, k, 0, k, seed=seed, stream=stream_a, dtype=np.float64)

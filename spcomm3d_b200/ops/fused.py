@@ -243,13 +243,13 @@ class FusedSDDMM(_FusedBase):
             raise ValueError("more than 2^25 owned rows on one rank")
         row_ranks = np.asarray(_peer_ranks(p, "row"), dtype=np.int64)
         if self.stage_a:
-            refs = (self.rank << 25) | np.arange(p.row.n_local, dtype=np.int64)
+            refs = None    # every A row the kernel touches is in my own block: no reference table
         else:
             refs = np.concatenate([(self.rank << 25) | np.arange(p.row.n_owned, dtype=np.int64),
                                    (row_ranks[p.row.recv_peer] << 25) | p.row.recv_src_idx.astype(np.int64)])
         _, a_need = self._side_tables(p.row, "A")
         self.a_src = self._dev_i64(a_need if a_need.size else [0])
-        self.a_refs = self._dev_i32(refs if refs.size else [0])
+        self.a_refs = None if refs is None else self._dev_i32(refs if refs.size else [0])
         self.a_bases = self._dev_i64([h.addr("A", r) for r in range(h.world)])
         self.b_src = self._dev_i64(b_need if b_need.size else [0])
         self.zwidth = p.nnz // Z + (1 if p.nnz % Z else 0)
@@ -272,12 +272,16 @@ class FusedSDDMM(_FusedBase):
         a.n_recv_a, a.a_src = n_recv_a, self.a_src.data_ptr()
         a.A_stage = self._A_full.data_ptr() + p.row.n_owned * self.row_bytes
         a.pull_order, a.n_waves, a.tiles_per_wave, a.wave_nnz = None, 0, 0, None
+        self.value_order = None   # None: results are stored in the plan's CSR order
         if overlap and (p.col.n_recv + n_recv_a) > 0 and p.nnz > 0:
             order, wave_nnz = self._plan_waves(p, n_recv_a)
+            # the kernel walks the nonzeros class by class and stores its values in that order: `value_order`
+            # is the storage order of this op's result (position in the plan's CSR order of every value)
+            self.value_order = order
             self._perm = (self._dev_i32(p.rowidx[order]), self._dev_i32(p.colidx[order]),
-                          torch.from_numpy(p.vals[order]).to(device=self.device, dtype=torch.float32),
-                          self._dev_i32(order))
-            a.rowidx, a.colidx, a.sval, a.orig = (t.data_ptr() for t in self._perm)
+                          torch.from_numpy(p.vals[order]).to(device=self.device, dtype=torch.float32))
+            a.rowidx, a.colidx, a.sval = (t.data_ptr() for t in self._perm)
+            a.orig = None
             a.nnz_free = int(wave_nnz[0])
             a.work_per_pull = 1
             a.wave_nnz = self._wave_nnz.data_ptr()
@@ -285,7 +289,8 @@ class FusedSDDMM(_FusedBase):
         else:
             a.rowidx, a.colidx, a.sval = op.rowidx.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
             a.orig, a.nnz_free, a.work_per_pull = None, 0, 1 << 30
-        a.a_refs, a.a_bases, a.world = self.a_refs.data_ptr(), self.a_bases.data_ptr(), h.world
+        a.a_refs = None if self.a_refs is None else self.a_refs.data_ptr()
+        a.a_bases, a.world = self.a_bases.data_ptr(), h.world
         a.B_loc, a.ldb = self.B_loc.data_ptr(), k
         a.n_owned_b, a.n_recv_b = p.col.n_owned, p.col.n_recv
         a.b_src = self.b_src.data_ptr()
@@ -309,7 +314,7 @@ class FusedSDDMM(_FusedBase):
         if direct_push is None and "SP3_FUSED_PUSH" in os.environ:
             direct_push = int(os.environ["SP3_FUSED_PUSH"])
         if direct_push is None:
-            direct_push = 1 if k >= 64 else (2 if not a.orig else 0)
+            direct_push = 2 if not a.orig else (1 if k >= 64 else 0)
         direct_push = int(direct_push)
         if direct_push == 2 and a.orig:
             direct_push = 0
@@ -327,7 +332,7 @@ class FusedSDDMM(_FusedBase):
         Tiles of A rows and tiles of B rows are interleaved in proportion, so that both operands arrive at the
         same relative pace and a nonzero whose two rows come early in their receive lists is ready early."""
         if target_waves is None:
-            target_waves = int(os.environ.get("SP3_FUSED_WAVES", "16"))
+            target_waves = int(os.environ.get("SP3_FUSED_WAVES", "4"))
         target_waves = max(1, min(MAX_WAVES, target_waves))
         n_a, n_b = -(-n_recv_a // PULL_ROWS), -(-p.col.n_recv // PULL_ROWS)
         n_pull = n_a + n_b

@@ -60,8 +60,8 @@ def test_fused_sddmm_all_ranks_one_gpu(meshstr, gen, k, overlap, push, stage_a, 
             op._fused.check()
             p = op.plan
             off, ln = p.owned_nnz_slice()
-            mine = CooMatrix(m.nrows, m.ncols, p.global_rows()[off:off + ln], p.global_cols()[off:off + ln],
-                             p.vals[off:off + ln])
+            pos = op.owned_positions()
+            mine = CooMatrix(m.nrows, m.ncols, p.global_rows()[pos], p.global_cols()[pos], p.vals[pos])
             ref = oracle.sddmm_ref(mine, Ae, Be)
             got = op._fused.out[:op._fused.out_len]
             got = got[off:off + ln] if mesh.Z == 1 else got

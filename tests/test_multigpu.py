@@ -44,8 +44,8 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
             c = sd.run()
             y = sp.run()
             off, ln = plan.owned_nnz_slice()
-            mine = CooMatrix(m.nrows, m.ncols, plan.global_rows()[off:off + ln], plan.global_cols()[off:off + ln],
-                             plan.vals[off:off + ln])
+            pos = sd.owned_positions()
+            mine = CooMatrix(m.nrows, m.ncols, plan.global_rows()[pos], plan.global_cols()[pos], plan.vals[pos])
             ref = oracle.sddmm_ref(mine, A, B)
             assert c.shape[0] == ln
             if ln:
@@ -76,8 +76,8 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
                 sd.poison_unowned()
                 c = sd.run_async()   # no status check here: nothing may raise while the buffer is bound
                 off, ln = plan.owned_nnz_slice()
-                mine = CooMatrix(m.nrows, m.ncols, plan.global_rows()[off:off + ln], plan.global_cols()[off:off + ln],
-                                 plan.vals[off:off + ln])
+                pos = sd.owned_positions()
+                mine = CooMatrix(m.nrows, m.ncols, plan.global_rows()[pos], plan.global_cols()[pos], plan.vals[pos])
                 ref = oracle.sddmm_ref(mine, A, B)
                 if c.shape[0] != ln or (ln and not bool(
                         (c.cpu().double() - ref).abs().max() <= 2e-5 * max(1.0, ref.abs().max()) * k ** 0.5)):
