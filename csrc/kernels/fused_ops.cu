@@ -577,11 +577,19 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
                 const int t = warp_ticket(c.ctrl + C_TICKET_FIN, lane);
                 if (t >= n_chunks) break;
                 const long long e0 = (long long)t * REDUCE_ELEMS;
-                for (long long j = e0 + lane; j < e0 + REDUCE_ELEMS && j < my_len; j += 32) {
-                    float s = 0.f;  // fiber ranks in ascending order; my own partial comes from `part`
-                    for (int z = 0; z < a.Z; ++z)
-                        s += z == a.my_z ? __ldcg(own + j) : __ldcg(mine + (long long)z * a.zwidth + j);
-                    a.out[j] = s;
+                const long long e1 = e0 + REDUCE_ELEMS < my_len ? e0 + REDUCE_ELEMS : my_len;
+                // four values per lane and step, so that 4 * Z independent loads are in flight per lane
+                for (long long j = e0 + lane; j < e1; j += 128) {
+                    float s[4] = {0.f, 0.f, 0.f, 0.f};  // fiber ranks in ascending order; my own partial comes from `part`
+                    for (int z = 0; z < a.Z; ++z) {
+                        const float* src = z == a.my_z ? own : mine + (long long)z * a.zwidth;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (j + 32 * q < e1) s[q] += __ldcg(src + j + 32 * q);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (j + 32 * q < e1) a.out[j + 32 * q] = s[q];
                 }
             }
         }
@@ -784,14 +792,35 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
             const int r0 = t * REDUCE_ROWS;
             const int r1 = r0 + REDUCE_ROWS < a.n_crows ? r0 + REDUCE_ROWS : a.n_crows;
             const int total = (r1 - r0) * a.nvec;
-            for (int e = lane; e < total; e += 32) {
-                const int ci = r0 + e / a.nvec, v = e % a.nvec;
-                const int row = __ldg(a.crows + ci);
-                float4* y = Yv + (long long)row * ldy_v + v;
-                float4 s = *y;
-                for (long long p = a.cptr[ci]; p < a.cptr[ci + 1]; ++p)
-                    vadd(s, __ldcg(Sv + (long long)a.cslot[p] * lds_v + v));
-                *y = s;
+            // two elements per lane and step: their loads (own row, slot rows) are independent and overlap
+            for (int e = lane; e < total; e += 64) {
+                float4 s[2];
+                float4* y[2];
+                long long p0[2], p1[2];
+                int vv[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int eq = e + 32 * q;
+                    y[q] = nullptr;
+                    if (eq < total) {
+                        const int ci = r0 + eq / a.nvec;
+                        vv[q] = eq % a.nvec;
+                        y[q] = Yv + (long long)__ldg(a.crows + ci) * ldy_v + vv[q];
+                        p0[q] = __ldg(a.cptr + ci);
+                        p1[q] = __ldg(a.cptr + ci + 1);
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    if (y[q]) s[q] = *y[q];
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    if (y[q])
+                        for (long long p = p0[q]; p < p1[q]; ++p)
+                            vadd(s[q], __ldcg(Sv + (long long)__ldg(a.cslot + p) * lds_v + vv[q]));
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    if (y[q]) *y[q] = s[q];
             }
         }
         finish_epilogue(c, lane, nwarps);

@@ -50,6 +50,8 @@ def main(argv=None):
     ap.add_argument("--rank", type=int, default=0, help="rank whose MAIN phase is timed")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--only", default=None, choices=["sddmm", "spmm"])
+    ap.add_argument("--no-overlap", action="store_true", help="SDDMM: compute only after all pulls (no reordering)")
     args = ap.parse_args(argv)
     mesh = Mesh3D.parse(args.mesh)
     m = generate.from_spec(args.gen, seed=args.seed)
@@ -57,8 +59,11 @@ def main(argv=None):
     fabric = LocalFabric(mesh.size)
     kl = [split_k(args.k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
     for cls, F in ((DistSDDMM, FusedSDDMM), (DistSpMM, FusedSpMM)):
+        if args.only and args.only != cls.kernel:
+            continue
+        kw = {"overlap": False} if (args.no_overlap and cls is DistSDDMM) else {}
         heaps = fabric.heaps([F.region_sizes(plans[r], kl[r]) for r in range(mesh.size)])
-        ops = [cls(plans[r], None, args.k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=5.0)
+        ops = [cls(plans[r], None, args.k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=5.0, **kw)
                for r in range(mesh.size)]
         for op in ops:
             for name, side, st in (("A_owned", op.plan.row, 1), ("B_owned", op.plan.col, 2),

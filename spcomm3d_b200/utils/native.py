@@ -230,7 +230,8 @@ def cuda():
     code paths never fall back silently to another implementation."""
     global _cuda
     if _cuda is None:
-        path = build_cuda()
+        # SP3_CUDA_LIB: load this build of the kernel library instead (tuning builds with other compile-time knobs)
+        path = os.environ.get("SP3_CUDA_LIB") or build_cuda()
         _cuda = ctypes.CDLL(str(path))
         from .cuda_sigs import CUDA_SIGS
         _bind(_cuda, CUDA_SIGS)
