@@ -83,6 +83,10 @@ void summarize(const std::vector<uint64_t>& v, double* avg, double* mx) {
 SP3_API int sp3_serial_sim(uint64_t nnz, const uint32_t* rows, const uint32_t* cols, uint64_t M, uint64_t N,
                            uint32_t X, uint32_t Y, uint64_t seed, int policy, int mode, double* out) {
     if (X == 0 || Y == 0) return sp3::E_ARG;
+    // mode + 16: the dense method is counted as the reference's simulator counts it (serialSim.cpp:233-247):
+    // one message to, and one copy of the own block for, every other rank of the line
+    const bool p2p_dense = (mode & 16) != 0;
+    mode &= 15;
     const uint32_t P = X * Y;
     std::vector<int32_t> rowmap(M), colmap(N);
     sp3_rr_map(M, X, seed, 101, rowmap.data());
@@ -108,6 +112,10 @@ SP3_API int sp3_serial_sim(uint64_t nnz, const uint32_t* rows, const uint32_t* c
         drv[p] = (useR ? R.line_size[x] - R.owned[p] : 0) + (useC ? Cc.line_size[y] - Cc.owned[p] : 0);
         dsm[p] = (useR ? 1 : 0) + (useC ? 1 : 0);
         drm[p] = (useR ? Y - 1 : 0) + (useC ? X - 1 : 0);
+        if (p2p_dense) {
+            dsv[p] = (useR ? R.owned[p] * (Y - 1) : 0) + (useC ? Cc.owned[p] * (X - 1) : 0);
+            dsm[p] = drm[p];
+        }
     }
     summarize(sm, &out[0], &out[4]); summarize(sv, &out[1], &out[5]);
     summarize(rm, &out[2], &out[6]); summarize(rv, &out[3], &out[7]);

@@ -81,8 +81,10 @@ class Runtime:
 
     def variants(self, args, default):
         v = args.variant.split(",") if args.variant else list(default)
-        if self.device.type != "cuda" or self.dtype != torch.float32:
+        if self.device.type != "cuda":
             v = [x for x in v if not x.startswith("fused")]
+        if self.dtype != torch.float32:   # the in-switch reduction is built for fp32 only
+            v = [x for x in v if x != "fused-multimem"]
         if "fused-multimem" in v and self.mesh.Z != self.world:
             # a multicast binding over part of the job has not been proven on real switches
             self.say(f"# skipping fused-multimem on {self.mesh}: limited to meshes whose Z fiber is the whole job")

@@ -290,6 +290,10 @@ class DistSpMM(_Dist3DOp):
             self.Y_owned = self.Y_loc[:p.row.n_owned]
         elif variant == "fused" and self._fused.atomic:
             self.Y_owned = self._fused.Y_heap   # peers add their partial rows into it
+        elif variant == "fused":
+            # same padded leading dimension as the kernel's other dense blocks (any k / Z)
+            self.Y_owned = torch.zeros(p.row.n_owned, self._fused.kpad, dtype=dtype,
+                                       device=self.device)[:, :self.k_loc]
         else:
             self.Y_owned = torch.zeros(p.row.n_owned, self.k_loc, dtype=dtype, device=self.device)
         self.sched = None

@@ -130,7 +130,7 @@ class SddmmSpmmStep:
         sd, sp, p = self.sddmm, self.spmm, self.plan
         dev, dt, kl = self.device, sd.dtype, sd.k_loc
         f = getattr(sd, "_fused", None)
-        A = f._A_full if f is not None else sd.A_loc
+        A = f._A_full[:, :kl] if f is not None else sd.A_loc
         Y = torch.empty(p.row.n_local, kl, dtype=dt, device=dev)
         sched = sp.sched
         if sched is None and dev.type == "cuda":

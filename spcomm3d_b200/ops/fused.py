@@ -62,7 +62,7 @@ class _SpmmArgs(C.Structure):
                 ("X_loc", P), ("ldx", C.c_longlong), ("n_owned_x", C.c_int), ("n_recv_x", C.c_int),
                 ("x_src", P), ("nvec", C.c_int), ("lg", _SpmmLong), ("n_owned_y", C.c_int), ("n_crows", C.c_int),
                 ("crows", P), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
-                ("ldy", C.c_longlong), ("beta", C.c_float), ("cptr", P), ("cslot", P), ("slots", P),
+                ("ldy", C.c_longlong), ("beta", C.c_double), ("cptr", P), ("cslot", P), ("slots", P),
                 ("lds", C.c_longlong), ("atomic", C.c_int), ("red_v4", C.c_int), ("crow_flag", P),
                 ("bulk_pull", C.c_int)]
 
@@ -85,6 +85,18 @@ def _check_layout():
 
 class FusedStatusError(RuntimeError):
     pass
+
+
+def _esize(dtype) -> int:
+    return 8 if dtype == torch.float64 else 4
+
+
+def _pad4(k: int, dtype=torch.float32) -> int:
+    """Leading dimension of the dense blocks of the fused kernels: k rounded up so that a row is a whole number
+    of 16-byte vectors (4 fp32 or 2 fp64 values) for any k / Z.  The padding columns are zero and stay zero:
+    they add nothing to a dot product and produce zeros in a result row."""
+    per = 16 // _esize(dtype)
+    return (int(k) + per - 1) // per * per
 
 
 def _bulk_default(bulk_pull):
@@ -113,14 +125,17 @@ class _FusedBase:
         self.op, self.plan = op, op.plan
         self.device = op.device
         self.k_loc = op.k_loc
-        if op.dtype != torch.float32:
-            raise ValueError("fused kernels are fp32")
-        if self.k_loc % 4 or self.k_loc == 0 or self.k_loc > 1024:
-            raise ValueError(f"fused kernels need k/Z to be a multiple of 4 (got {self.k_loc})")
+        if op.dtype not in (torch.float32, torch.float64):
+            raise ValueError("fused kernels are fp32 or fp64")
+        self.dtype, self.es = op.dtype, _esize(op.dtype)
+        kmax = 4096 // self.es   # a dense row is at most 256 16-byte vectors
+        if self.k_loc == 0 or self.k_loc > kmax:
+            raise ValueError(f"fused kernels need 1 <= k/Z <= {kmax} for this value type (got {self.k_loc})")
         if self.plan.mesh.size > MAX_RANKS:
             raise ValueError(f"fused kernels support at most {MAX_RANKS} ranks")
-        self.row_bytes = self.k_loc * 4
-        self.nvec = self.k_loc // 4
+        self.kpad = _pad4(self.k_loc, self.dtype)     # leading dimension of every dense block, slot and carry row
+        self.row_bytes = self.kpad * self.es
+        self.nvec = self.row_bytes // 16
         if heap is None:
             if fabric is None:
                 fabric = IpcFabric(device=self.device)
@@ -136,7 +151,10 @@ class _FusedBase:
         self._keep = []
 
     def region_sizes_for(self, plan, k_loc):
-        return self.region_sizes(plan, k_loc)
+        return self.region_sizes(plan, k_loc, dtype=self.dtype)
+
+    def _fn(self, kernel: str):
+        return getattr(native.cuda(), f"sp3_fused_{kernel}_{'f64' if self.dtype == torch.float64 else 'f32'}")
 
     def _dev_i64(self, values):
         return torch.from_numpy(np.asarray(values, dtype=np.int64).reshape(-1)).to(self.device)
@@ -207,12 +225,13 @@ class _FusedBase:
 
 class FusedSDDMM(_FusedBase):
     @staticmethod
-    def region_sizes(plan, k_loc: int) -> dict:
-        rb = k_loc * 4
+    def region_sizes(plan, k_loc: int, dtype=torch.float32) -> dict:
+        es = _esize(dtype)
+        rb = _pad4(k_loc, dtype) * es
         Z = plan.mesh.Z
         zwidth = plan.nnz // Z + (1 if plan.nnz % Z else 0)
         return {"pad": F_KINDS * MAX_RANKS * 4, "A": plan.row.n_local * rb, "B": plan.col.n_local * rb,
-                "zbuf": 2 * Z * zwidth * 4 if Z > 1 else 0}
+                "zbuf": 2 * Z * zwidth * es if Z > 1 else 0}
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
                  overlap: bool = True, direct_push: bool | None = None, stage_a: bool | None = None,
@@ -234,9 +253,11 @@ class FusedSDDMM(_FusedBase):
         if stage_a is None:
             stage_a = os.environ.get("SP3_FUSED_STAGE_A", "1") == "1"
         self.stage_a = bool(stage_a)
-        self._A_full = h.view("A", torch.float32, (p.row.n_local, k))
-        self.A_loc = self._A_full[:p.row.n_owned]
-        self.B_loc = h.view("B", torch.float32, (p.col.n_local, k))
+        kp = self.kpad
+        self._A_full = h.view("A", self.dtype, (p.row.n_local, kp))   # padded storage, see _pad4
+        self._B_full = h.view("B", self.dtype, (p.col.n_local, kp))
+        self.A_loc = self._A_full[:p.row.n_owned, :k]
+        self.B_loc = self._B_full[:, :k]
         _, b_need = self._side_tables(p.col, "B")
         # A rows stay where they are: reference = owner rank << 25 | row inside the owner's block
         if max(int(p.row.peer_owned.max(initial=0)), p.row.n_owned) >= 1 << 25:
@@ -256,7 +277,7 @@ class FusedSDDMM(_FusedBase):
         fiber = _peer_ranks(p, "fiber")
         self.zbuf_ptrs = self._dev_i64([h.addr("zbuf", r) for r in fiber])
         self.out_len = p.nnz if Z == 1 else p.owned_nnz_slice()[1]
-        self.out = torch.zeros(max(self.out_len, 1), dtype=torch.float32, device=self.device)
+        self.out = torch.zeros(max(self.out_len, 1), dtype=self.dtype, device=self.device)
         a = self.args = _SddmmArgs()
         row_r, col_r = _peer_ranks(p, "row"), _peer_ranks(p, "col")
         read_from = [row_r[q] for q in range(p.row.npeers) if p.row.recv_counts[q] > 0] + \
@@ -279,7 +300,7 @@ class FusedSDDMM(_FusedBase):
             # is the storage order of this op's result (position in the plan's CSR order of every value)
             self.value_order = order
             self._perm = (self._dev_i32(p.rowidx[order]), self._dev_i32(p.colidx[order]),
-                          torch.from_numpy(p.vals[order]).to(device=self.device, dtype=torch.float32))
+                          torch.from_numpy(p.vals[order]).to(device=self.device, dtype=self.dtype))
             a.rowidx, a.colidx, a.sval = (t.data_ptr() for t in self._perm)
             a.orig = None
             a.nnz_free = int(wave_nnz[0])
@@ -291,7 +312,7 @@ class FusedSDDMM(_FusedBase):
             a.orig, a.nnz_free, a.work_per_pull = None, 0, 1 << 30
         a.a_refs = None if self.a_refs is None else self.a_refs.data_ptr()
         a.a_bases, a.world = self.a_bases.data_ptr(), h.world
-        a.B_loc, a.ldb = self.B_loc.data_ptr(), k
+        a.B_loc, a.ldb = self._B_full.data_ptr(), kp
         a.n_owned_b, a.n_recv_b = p.col.n_owned, p.col.n_recv
         a.b_src = self.b_src.data_ptr()
         a.nvec = self.nvec
@@ -302,9 +323,11 @@ class FusedSDDMM(_FusedBase):
         a.out = self.out.data_ptr()
         self._mc = None
         if Z > 1 and self.zreduce == "multimem":
+            if self.dtype != torch.float32:
+                raise ValueError("zreduce='multimem' is built for fp32")
             self.part, a.mc_part, a.part_stride = self._multicast_part(op, p.nnz)
         else:
-            self.part = torch.zeros(p.nnz if Z > 1 else 1, dtype=torch.float32, device=self.device)
+            self.part = torch.zeros(p.nnz if Z > 1 else 1, dtype=self.dtype, device=self.device)
             a.mc_part, a.part_stride = None, 0
         a.part = self.part.data_ptr()
         # Push mode of the partial values (Z > 1).  1: remote stores as the values are computed -- a lane group
@@ -314,7 +337,7 @@ class FusedSDDMM(_FusedBase):
         if direct_push is None and "SP3_FUSED_PUSH" in os.environ:
             direct_push = int(os.environ["SP3_FUSED_PUSH"])
         if direct_push is None:
-            direct_push = 2 if not a.orig else (1 if k >= 64 else 0)
+            direct_push = 2 if not a.orig else (1 if self.row_bytes >= 256 else 0)
         direct_push = int(direct_push)
         if direct_push == 2 and a.orig:
             direct_push = 0
@@ -388,7 +411,7 @@ class FusedSDDMM(_FusedBase):
     def launch(self, phases=PH_ALL, new_epoch=True):
         if new_epoch:
             self.epoch += 1
-        self._launch(native.cuda().sp3_fused_sddmm_f32, phases)
+        self._launch(self._fn("sddmm"), phases)
 
     def run(self):
         self.launch()
@@ -402,8 +425,8 @@ class FusedSpMM(_FusedBase):
     pass, results depend on the order of the additions."""
 
     @staticmethod
-    def region_sizes(plan, k_loc: int, reduce: str | None = None) -> dict:
-        rb = k_loc * 4
+    def region_sizes(plan, k_loc: int, reduce: str | None = None, dtype=torch.float32) -> dict:
+        rb = _pad4(k_loc, dtype) * _esize(dtype)
         if reduce is None:
             reduce = os.environ.get("SP3_FUSED_SPMM_REDUCE", "slots")
         if reduce == "atomic":
@@ -413,7 +436,7 @@ class FusedSpMM(_FusedBase):
                 "slots": 2 * _align(plan.row.n_send * rb)}
 
     def region_sizes_for(self, plan, k_loc):
-        return self.region_sizes(plan, k_loc, self.reduce)
+        return self.region_sizes(plan, k_loc, self.reduce, dtype=self.dtype)
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
                  reduce: str | None = None, red_v4: bool | None = None, bulk_pull: bool | None = None):
@@ -430,7 +453,9 @@ class FusedSpMM(_FusedBase):
         rp = p.row
         if self.atomic and "Y" not in h.sizes:
             raise ValueError("the heap was sized for reduce='slots'")
-        self.X_loc = h.view("X", torch.float32, (p.col.n_local, k))
+        kp = self.kpad
+        self._X_full = h.view("X", self.dtype, (p.col.n_local, kp))   # padded storage, see _pad4
+        self.X_loc = self._X_full[:, :k]
         # no local Y block: owned rows are written straight into the result, the others into their owners' slots
         self.Y_loc = None
         _, x_need = self._side_tables(p.col, "X")
@@ -444,7 +469,7 @@ class FusedSpMM(_FusedBase):
         slot_row = rp.push_offset[rp.recv_peer] + i_in_seg
         if self.atomic:
             _, y_dst = self._side_tables(rp, "Y")   # address of every row I do not own inside its owner's Y
-            self.Y_heap = h.view("Y", torch.float32, (rp.n_owned, k))
+            self.Y_heap = h.view("Y", self.dtype, (rp.n_owned, kp))[:, :k]
         else:
             base = np.asarray(h.peer_base, dtype=np.int64) + h.offsets["slots"]
             y_dst = base[np.asarray(row_r, dtype=np.int64)[rp.recv_peer]] + slot_row * rb
@@ -460,8 +485,8 @@ class FusedSpMM(_FusedBase):
         self.crows = self._dev_i32(crows if crows.size else [0])
         self.cslot = self._dev_i32(order if order.size else [0])
         self.sched = cuda_ops.SpmmSchedule(op.rowptr)
-        carry, ldc = self.sched.carry_for(k, torch.float32, self.device)
-        self.slots = h.view("slots", torch.float32, (h.sizes["slots"] // 4,))
+        carry, ldc = self.sched.carry_for(kp, self.dtype, self.device)
+        self.slots = h.view("slots", self.dtype, (h.sizes["slots"] // self.es,))
         flag = np.zeros(max(1, rp.n_owned), np.uint8)
         flag[crows] = 1
         self.crow_flag = torch.from_numpy(flag).to(self.device)
@@ -473,21 +498,21 @@ class FusedSpMM(_FusedBase):
         self._fill_comm(a.comm, read_from, readers, push_to, contrib)
         a.nitems, a.items = self.sched.items.shape[0], self.sched.items.data_ptr()
         a.rowptr, a.colidx, a.val = op.rowptr.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
-        a.X_loc, a.ldx = self.X_loc.data_ptr(), k
+        a.X_loc, a.ldx = self._X_full.data_ptr(), kp
         a.n_owned_x, a.n_recv_x = p.col.n_owned, p.col.n_recv
         a.x_src = self.x_src.data_ptr()
         a.nvec = self.nvec
         a.lg.first_piece, a.lg.npieces = self.sched.first.data_ptr(), self.sched.npieces.data_ptr()
         a.lg.counters = self.sched.counters.data_ptr()
         a.lg.carry = carry.data_ptr() if carry is not None else None
-        a.lg.ldc = ldc if carry is not None else k
+        a.lg.ldc = ldc if carry is not None else kp
         a.lg.piece_len = self.sched.piece_len
         a.n_owned_y = rp.n_owned
         a.n_crows, a.crows = int(crows.size), self.crows.data_ptr()
         a.y_dst = self.y_dst.data_ptr()
         a.parity_off_v = half // 16
         a.cptr, a.cslot = self.cptr.data_ptr(), self.cslot.data_ptr()
-        a.slots, a.lds = self.slots.data_ptr(), k
+        a.slots, a.lds = self.slots.data_ptr(), kp
         a.atomic, a.red_v4, a.crow_flag = int(self.atomic), int(bool(red_v4)), self.crow_flag.data_ptr()
         if self.atomic:
             a.parity_off_v = 0
@@ -499,8 +524,12 @@ class FusedSpMM(_FusedBase):
         a = self.args
         if self.atomic and Y.data_ptr() != self.Y_heap.data_ptr():
             raise ValueError("reduce='atomic': the result must be this op's Y_heap (peers add into it)")
-        a.Y, a.ldy, a.beta = Y.data_ptr(), Y.stride(0) if Y.shape[0] > 1 else self.k_loc, float(beta)
-        self._launch(native.cuda().sp3_fused_spmm_f32, phases)
+        ldy = Y.stride(0) if Y.shape[0] > 1 else self.kpad
+        if (ldy * self.es) % 16 or ldy < self.kpad or Y.data_ptr() % 16 or Y.dtype != self.dtype:
+            raise ValueError(f"the result needs a 16-byte aligned base, rows that are a multiple of 16 bytes apart "
+                             f"and a leading dimension of at least {self.kpad} (use DistSpMM.Y_owned)")
+        a.Y, a.ldy, a.beta = Y.data_ptr(), ldy, float(beta)
+        self._launch(self._fn("spmm"), phases)
 
     def run(self, Y: torch.Tensor, beta: float = 0.0):
         self.launch(Y, beta)

@@ -28,11 +28,13 @@ def find_xy(P: int) -> tuple[int, int]:
 
 
 def serial_sim(m: CooMatrix, X: int, Y: int, seed: int = 0, policy: str = "respect_comm",
-               mode: str = "sddmm") -> dict:
+               mode: str = "sddmm", dense_as_messages: bool = False) -> dict:
+    """dense_as_messages: count the dense method as one message and one copy of the own block per other rank
+    of the line (the reference simulator's closed form, serialSim.cpp:233-247) instead of one broadcast."""
     out = np.zeros(16, np.float64)
     rc = native.host().sp3_serial_sim(m.nnz, native.ptr(m.rows), native.ptr(m.cols), m.nrows, m.ncols, X, Y,
-                                      seed, {"respect_comm": 0, "random": 1}[policy], MODES[mode],
-                                      native.ptr(out))
+                                      seed, {"respect_comm": 0, "random": 1}[policy],
+                                      MODES[mode] + (16 if dense_as_messages else 0), native.ptr(out))
     native.check(rc, "serial_sim")
     return {"sparse": dict(zip(SIM_FIELDS, out[:8].tolist())), "dense": dict(zip(SIM_FIELDS, out[8:].tolist()))}
 
@@ -41,6 +43,22 @@ def sim_line(tag: str, m: CooMatrix, P: int, stats: dict) -> str:
     """One report line: `<tag S|B> <matrix> <P> <nnz> <8 fields>` (the S / B
     lines of serialSim.cpp:227-230,249-252)."""
     return f"{tag} {m.name} {P} {m.nnz} " + " ".join(f"{stats[f]:.2f}" for f in SIM_FIELDS)
+
+
+def find_xy_ref(P: int) -> tuple[int, int]:
+    """X x Y as the reference's simulator picks it: X the largest divisor of P not above sqrt(P), Y = P / X
+    (serialSim.cpp:100-106)."""
+    y, x = find_xy(P)
+    return x, y
+
+
+def sim_line_ref(tag: str, m: CooMatrix, N: int, X: int, Y: int, Z: int, f: int, stats: dict) -> str:
+    """The line the reference's simulator prints (serialSim.cpp:227-230, 249-252):
+    `name rows cols nnz N XxYxZ f c S|B avgSendMsgs avgSendVol avgRecvMsgs avgRecvVol maxSendMsgs maxSendVol
+    maxRecvMsgs maxRecvVol`, averages with two decimals, maxima as integers, volumes in dense rows."""
+    avg = " ".join(f"{stats[k]:.2f}" for k in SIM_FIELDS[:4])
+    mx = " ".join(str(int(round(stats[k]))) for k in SIM_FIELDS[4:])
+    return f"{m.name} {m.nrows} {m.ncols} {m.nnz} {N} {X}x{Y}x{Z} {f} {Z} {tag} {avg} {mx}"
 
 
 def count_excess(m: CooMatrix, X: int, Y: int, seed: int = 0) -> dict:

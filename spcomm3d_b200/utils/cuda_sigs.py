@@ -27,6 +27,8 @@ CUDA_SIGS = {
     "sp3_fused_struct_sizes": ("int", "p p p"),
     "sp3_fused_sddmm_f32": ("int", "p p"),
     "sp3_fused_spmm_f32": ("int", "p p"),
+    "sp3_fused_sddmm_f64": ("int", "p p"),
+    "sp3_fused_spmm_f64": ("int", "p p"),
     "sp3_fused_ctrl_words": ("int", ""),
     "sp3_symm_alloc": ("int", "u64 p"),
     "sp3_symm_free": ("int", "p"),

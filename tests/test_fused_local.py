@@ -123,6 +123,116 @@ def test_fused_spmm_all_ranks_one_gpu(meshstr, gen, k, reduce, red_v4, bulk):
             assert (op.Y_owned - y0).abs().max() <= 1e-5 * max(1.0, float(y0.abs().max()))
 
 
+@pytest.mark.parametrize("meshstr,k", [("2x2x2", 30), ("1x1x8", 30), ("2x1x2", 7), ("3x2x1", 50)])
+def test_fused_kernels_any_inner_dimension(meshstr, k):
+    """k / Z that is not a multiple of 4, and k that Z does not divide (fiber ranks then hold slices of
+    different widths, as the reference allows: floc = k / Z (+1), miniapp/bench_spmm.cpp:167-172): the dense
+    blocks get a leading dimension rounded up to 4 with zero padding."""
+    from spcomm3d_b200.models.dist_ops import DistSDDMM, DistSpMM
+    from spcomm3d_b200.ops import oracle
+    from spcomm3d_b200.ops.fused import FusedSDDMM, FusedSpMM, run_lockstep
+    from spcomm3d_b200.parallel.mesh import split_k
+    from spcomm3d_b200.parallel.symm import LocalFabric
+    from spcomm3d_b200.utils.sparse import CooMatrix
+    mesh, m, plans, A, B = _setup(meshstr, "zipf:700:900:1.6:600", k)
+    kl = [split_k(k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
+    assert any(x % 4 for x in kl)
+    for cls, F in ((DistSDDMM, FusedSDDMM), (DistSpMM, FusedSpMM)):
+        fabric = LocalFabric(mesh.size)
+        heaps = fabric.heaps([F.region_sizes(plans[r], kl[r]) for r in range(mesh.size)])
+        ops = [cls(plans[r], None, k, torch.float32, "cuda", "fused", heap=heaps[r], timeout_s=2.0)
+               for r in range(mesh.size)]
+        for op in ops:
+            p = op.plan
+            if cls is DistSDDMM:
+                op.fill_owned(op.A_owned, p.row.owned_gids, seed=5, stream=1)
+                op.fill_owned(op.B_owned, p.col.owned_gids, seed=5, stream=2)
+            else:
+                op.fill_owned(op.X_owned, p.col.owned_gids, seed=5, stream=2)
+                op.Y_owned.fill_(float("nan"))
+            op.poison_unowned()
+        run_lockstep([op._fused for op in ops], [(op.Y_owned, 0.0) for op in ops] if cls is DistSpMM else None)
+        full = oracle.spmm_ref(m, B) if cls is DistSpMM else None
+        for op in ops:
+            op._fused.check()
+            p = op.plan
+            if cls is DistSDDMM:
+                pos = op.owned_positions()
+                mine = CooMatrix(m.nrows, m.ncols, p.global_rows()[pos], p.global_cols()[pos], p.vals[pos])
+                ref = oracle.sddmm_ref(mine, A, B)
+                got = op._fused.out[:op._fused.out_len].cpu().double()
+                tol = 2e-5 * max(1.0, float(ref.abs().max()) if ref.numel() else 1.0) * k ** 0.5
+            else:
+                ko, kw = split_k(k, mesh.Z, p.coords[2])
+                ref = full[p.row.owned_gids][:, ko:ko + kw]
+                got = op.Y_owned.cpu().double()
+                tol = 2e-5 * max(1.0, float(ref.abs().max()) if ref.numel() else 1.0) * 8
+            assert got.shape == ref.shape
+            if ref.numel():
+                assert (got - ref).abs().max() <= tol
+        del ops, heaps, fabric
+
+
+@pytest.mark.parametrize("meshstr,k,reduce", [("2x2x2", 32, "slots"), ("1x1x8", 20, "slots"), ("3x2x1", 33, "atomic"),
+                                              ("2x1x2", 64, "slots")])
+def test_fused_kernels_fp64(meshstr, k, reduce):
+    """The fused kernels in the reference's value type (real_t = double, src/basic.hpp:17), against the fp64
+    oracle to fp64 accuracy; run twice, the slot reduction must repeat bit for bit."""
+    from spcomm3d_b200.models.dist_ops import DistSDDMM, DistSpMM
+    from spcomm3d_b200.ops import oracle
+    from spcomm3d_b200.ops.fused import FusedSDDMM, FusedSpMM, run_lockstep
+    from spcomm3d_b200.parallel.mesh import split_k
+    from spcomm3d_b200.parallel.symm import LocalFabric
+    from spcomm3d_b200.utils.sparse import CooMatrix
+    mesh, m, plans, A, B = _setup(meshstr, "zipf:700:900:1.6:600", k)
+    kl = [split_k(k, mesh.Z, plans[r].coords[2])[1] for r in range(mesh.size)]
+    dt = torch.float64
+    for cls, F in ((DistSDDMM, FusedSDDMM), (DistSpMM, FusedSpMM)):
+        fabric = LocalFabric(mesh.size)
+        if cls is DistSpMM:
+            heaps = fabric.heaps([F.region_sizes(plans[r], kl[r], reduce, dtype=dt) for r in range(mesh.size)])
+            kw = {"reduce": reduce}
+        else:
+            heaps = fabric.heaps([F.region_sizes(plans[r], kl[r], dtype=dt) for r in range(mesh.size)])
+            kw = {}
+        ops = [cls(plans[r], None, k, dt, "cuda", "fused", heap=heaps[r], timeout_s=2.0, **kw)
+               for r in range(mesh.size)]
+        previous = None
+        for rep in range(2):
+            for op in ops:
+                p = op.plan
+                if cls is DistSDDMM:
+                    op.fill_owned(op.A_owned, p.row.owned_gids, seed=5, stream=1)
+                    op.fill_owned(op.B_owned, p.col.owned_gids, seed=5, stream=2)
+                else:
+                    op.fill_owned(op.X_owned, p.col.owned_gids, seed=5, stream=2)
+                    op.Y_owned.fill_(float("nan"))
+                op.poison_unowned()
+            run_lockstep([op._fused for op in ops], [(op.Y_owned, 0.0) for op in ops] if cls is DistSpMM else None)
+            full = oracle.spmm_ref(m, B) if cls is DistSpMM else None
+            results = []
+            for op in ops:
+                op._fused.check()
+                p = op.plan
+                if cls is DistSDDMM:
+                    pos = op.owned_positions()
+                    mine = CooMatrix(m.nrows, m.ncols, p.global_rows()[pos], p.global_cols()[pos], p.vals[pos])
+                    ref = oracle.sddmm_ref(mine, A, B)
+                    got = op._fused.out[:op._fused.out_len].cpu()
+                else:
+                    ko, kw_ = split_k(k, mesh.Z, p.coords[2])
+                    ref = full[p.row.owned_gids][:, ko:ko + kw_]
+                    got = op.Y_owned.cpu()
+                assert got.dtype == torch.float64 and got.shape == ref.shape
+                if ref.numel():
+                    assert (got - ref).abs().max() <= 1e-12 * max(1.0, float(ref.abs().max())) * k
+                results.append(got.clone())
+            if previous is not None and not (cls is DistSpMM and reduce == "atomic"):
+                assert all(torch.equal(x, y) for x, y in zip(results, previous))
+            previous = results
+        del ops, heaps, fabric
+
+
 def test_atomic_spmm_start_and_main_in_one_launch():
     """Atomic mode with START and MAIN in the same launch (what real ranks run): the rows that receive
     contributions are cleared by START warps with plain stores, and no warp -- of this rank either -- may add

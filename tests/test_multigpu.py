@@ -121,3 +121,38 @@ def test_all_variants_on_real_peers():
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     for meshstr in _meshes(n):
         run_ranks(_rank_main, n, meshstr, "zipf:3000:4000:1.6:700", 64, ["fused", "fused-atomic", "sparseNRB", "sparse", "dense"], backend="nccl")
+
+
+def test_bin_file_input_on_gpu_ranks(tmp_path):
+    """The reference's only input route -- a .bin file read collectively by all ranks
+    (src/parallel_io.hpp:132-190) -- on GPU ranks: the process group carries NCCL for device tensors and gloo
+    for the host arrays of the reader, the programmes run under torchrun as a user starts them, and the
+    distributed checksums equal the serial one."""
+    import subprocess
+    import sys
+    from dist_utils import ROOT, free_port
+    from spcomm3d_b200.cli import num_check_seq
+    from spcomm3d_b200.utils import binfmt, generate, stats
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    m = generate.fixed_degree(3000, 2500, 6, seed=4)
+    mtx, binp = str(tmp_path / "g.mtx"), str(tmp_path / "g.bin")
+    binfmt.write_mtx(mtx, m)
+    binfmt.conv2bin(mtx, binp)
+    serial = num_check_seq.checksum_of(mtx, 16)
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+
+    def torchrun(module, *args):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+               "--master-addr", "127.0.0.1", "--master-port", str(free_port()), "-m", module, *args]
+        return subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600, cwd=ROOT)
+
+    out = torchrun("spcomm3d_b200.cli.num_res_check", "-k", "16", "-c", "1", "--variant", "fused,sparseNRB", binp)
+    assert out.returncode == 0, out.stderr[-3000:]
+    sums = [float(l.rsplit("=", 1)[1]) for l in out.stdout.splitlines()
+            if l.startswith("Global numerical sum") and "sddmm" in l]
+    assert len(sums) == 2 and all(abs(s - serial) < 1e-4 * max(1.0, abs(serial)) for s in sums), (sums, serial)
+    out = torchrun("spcomm3d_b200.cli.bench_sddmm", "-k", "16", "-c", "1", "-i", "2", "--variant", "fused", binp)
+    assert out.returncode == 0, out.stderr[-3000:]
+    lines = [stats.parse_line(l) for l in out.stdout.splitlines() if l.startswith("g ")]
+    assert len(lines) == 2 * 2 and {l["alg"] for l in lines} == {"sparseNB sddmm PRE", "sparseNB sddmm POST"}
+    assert all(l["P"] == n for l in lines)

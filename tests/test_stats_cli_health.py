@@ -109,6 +109,49 @@ def test_single_process_tools(tmp_path):
     assert total == m.nnz
 
 
+def test_gpu_runtimes_start_a_group_with_a_host_backend(monkeypatch):
+    """The collective .bin reader exchanges host arrays; on GPU ranks the group must therefore carry gloo next
+    to NCCL.  Checked on the call the runtime makes (no GPU needed)."""
+    import argparse
+    import torch.distributed as dist
+    from spcomm3d_b200.cli import common
+    seen = {}
+    monkeypatch.setenv("WORLD_SIZE", "2")
+    monkeypatch.setenv("RANK", "0")
+    monkeypatch.setattr(common.torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(common.torch.cuda, "set_device", lambda d: None)
+
+    def fake_init(backend, **kw):
+        seen["backend"], seen["kw"] = backend, kw
+        raise RuntimeError("stop here")
+
+    monkeypatch.setattr(dist, "init_process_group", fake_init)
+    args = argparse.Namespace(device=None, mesh=None, Z=1, dtype=None)
+    with pytest.raises(RuntimeError, match="stop here"):
+        common.Runtime(args)
+    assert seen["backend"] == "cpu:gloo,cuda:nccl" and "device_id" in seen["kw"]
+
+
+def test_serial_sim_reference_line_layout(tmp_path, capsys):
+    """--ref-format: `name rows cols nnz N XxYxZ f c S|B 4 averages 4 integer maxima` (miniapp/serialSim.cpp:
+    227-230, 249-252), X <= Y as its findXY picks them, the dense line counted message by message, and the
+    density sweep 1e-7 ... 1e-3 under the name SYNTH (:278-287)."""
+    from spcomm3d_b200.cli import serial_sim
+    serial_sim.main(["-n", "16,32", "-i", "3000", "--density-sweep", "--ref-format", "-c", "2", "-k", "64"])
+    lines = [l.split() for l in capsys.readouterr().out.splitlines() if l and not l.startswith("#")]
+    assert len(lines) == 5 * 2 * 2
+    nnz_seen = set()
+    for t in lines:
+        assert len(t) == 17 and t[0] == "SYNTH" and t[1] == t[2] == "3000" and t[8] in ("S", "B")
+        N, (X, Y, Z) = int(t[4]), (int(v) for v in t[5].split("x"))
+        assert X * Y * Z == N and X <= Y and Z == 2 and t[6] == "64" and t[7] == "2"
+        assert all("." in v for v in t[9:13]) and all(v.isdigit() for v in t[13:17])
+        nnz_seen.add(int(t[3]))
+        if t[8] == "B":   # every rank sends to, and hears from, the X + Y - 2 other ranks of its two lines
+            assert float(t[9]) == float(t[11]) == X + Y - 2 and t[13] == t[15] == str(X + Y - 2)
+    assert sorted(nnz_seen) == [int(3000 * 3000 * 10.0 ** e) for e in range(-7, -2)]
+
+
 # ---- failure detection, all on the host -------------------------------------
 def _absent_peer(rank, world):
     """Rank 1 never joins the exchange; rank 0's collective must end with an
