@@ -118,6 +118,58 @@ SP3_API int sp3_gen_from_rowptr(uint64_t M, uint64_t N, const uint64_t* rowptr, 
     return bad ? sp3::E_ARG : sp3::OK;
 }
 
+// The same matrix as sp3_gen_from_rowptr restricted to one block of a 2D partition: rows with rowmap[r] == x,
+// columns with colmap[c] == y (a null map keeps everything on that side).  Every entry has the value it has in
+// the whole matrix (values are drawn by global position), so ranks that each generate their own block hold,
+// together, exactly the matrix a single generator call would give.  Two calls: with rows == null only the number
+// of entries is returned in *count; then the arrays of that length are filled (row-major, columns ascending).
+SP3_API int sp3_gen_from_rowptr_block(uint64_t M, uint64_t N, const uint64_t* rowptr, uint64_t seed,
+                                      const int32_t* rowmap, int32_t x, const int32_t* colmap, int32_t y,
+                                      uint64_t* count, uint32_t* rows, uint32_t* cols, double* vals) {
+    std::vector<uint64_t> start(M + 1, 0);
+    int bad = 0;
+#pragma omp parallel
+    {
+        std::vector<uint32_t> tmp;
+#pragma omp for schedule(dynamic, 4096)
+        for (int64_t r = 0; r < (int64_t)M; ++r) {
+            if (rowmap && rowmap[r] != x) continue;
+            const uint64_t b = rowptr[r], e = rowptr[r + 1];
+            if (e - b > N) { bad = 1; continue; }
+            if (!colmap) { start[r + 1] = e - b; continue; }
+            tmp.resize(e - b);
+            draw_distinct(seed, (uint64_t)r, (uint32_t)(e - b), N, tmp.data());
+            uint64_t kept = 0;
+            for (uint64_t s = 0; s < e - b; ++s) kept += colmap[tmp[s]] == y;
+            start[r + 1] = kept;
+        }
+    }
+    if (bad) return sp3::E_ARG;
+    for (uint64_t r = 0; r < M; ++r) start[r + 1] += start[r];
+    *count = start[M];
+    if (!rows) return sp3::OK;
+#pragma omp parallel
+    {
+        std::vector<uint32_t> tmp;
+#pragma omp for schedule(dynamic, 4096)
+        for (int64_t r = 0; r < (int64_t)M; ++r) {
+            if (start[r + 1] == start[r]) continue;
+            const uint64_t b = rowptr[r], e = rowptr[r + 1];
+            tmp.resize(e - b);
+            draw_distinct(seed, (uint64_t)r, (uint32_t)(e - b), N, tmp.data());
+            uint64_t o = start[r];
+            for (uint64_t s = 0; s < e - b; ++s) {
+                if (colmap && colmap[tmp[s]] != y) continue;
+                rows[o] = (uint32_t)r;
+                cols[o] = tmp[s];
+                vals[o] = sp3::u01(sp3::rnd(seed, S_VAL, b + s));
+                ++o;
+            }
+        }
+    }
+    return sp3::OK;
+}
+
 // R-MAT edge keys (row << 32 | col) for a 2^scale square graph; `nedges`
 // edges are drawn by `scale` quadrant choices with probabilities a,b,c,(d).
 // The caller removes duplicates with sp3_sort_unique_u64.

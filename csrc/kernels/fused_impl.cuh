@@ -197,7 +197,8 @@ __device__ __forceinline__ void pull_rows(int r0, int r1, const float4* const* _
 // store into the local block (the rows of a tile are consecutive there).  Nothing passes through registers and
 // the warp never stalls on a load, so a few warps keep NVLink busy while all the others compute.
 constexpr int BULK_STAGES = 3;
-constexpr unsigned BULK_STAGE_BYTES = 8192;
+constexpr unsigned BULK_STAGE_BYTES = 4096;   // 3 x 4 KB per block: two stages in flight per puller, 49 KB of an SM's
+                                               // shared memory with four resident blocks (the rest stays L1 cache)
 constexpr unsigned BULK_SMEM_BYTES = BULK_STAGES * BULK_STAGE_BYTES + 64;
 
 struct BulkRing {

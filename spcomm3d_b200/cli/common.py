@@ -108,6 +108,10 @@ class Runtime:
 
     def _build_plan(self, args):
         if args.gen:
+            if self.world > 1:   # every rank generates only its own block where the generator allows it
+                from ..parallel.plan import build_my_plan_from_spec
+                return build_my_plan_from_spec(args.gen, self.mesh, self.groups, seed=args.seed,
+                                               policy=args.policy)[1]
             m = generate.from_spec(args.gen, seed=args.seed)
             _, plan = build_my_plan(m, self.mesh, self.rank, seed=args.seed, policy=args.policy)
             return plan

@@ -43,8 +43,9 @@ def sample_sddmm_error(plan, c_owned: torch.Tensor, k: int, seed: int, stream_a:
 def sample_spmm_error(plan, m, y_owned: torch.Tensor, k: int, seed: int, stream_x: int,
                       n_rows: int = 256, max_nnz: int = 1 << 20, rng_seed: int = 0) -> float:
     """max |Y - Y_ref| / max |Y_ref| over a sample of this rank's owned rows of
-    Y = S X, my k slice.  `m` is the whole matrix (global ids): a row of Y sums
-    over all mesh columns, not only this rank's block."""
+    Y = S X, my k slice.  `m` is the whole matrix (global ids), or a function
+    that returns all entries of given global rows: a row of Y sums over all
+    mesh columns, not only this rank's block."""
     n_owned = plan.row.n_owned
     if n_owned == 0:
         return 0.0
@@ -52,6 +53,8 @@ def sample_spmm_error(plan, m, y_owned: torch.Tensor, k: int, seed: int, stream_
     rng = np.random.default_rng(rng_seed + 104729 * plan.rank)
     loc = np.sort(rng.choice(n_owned, size=min(n_rows, n_owned), replace=False))
     gids = plan.row.owned_gids[loc]
+    if callable(m):
+        m = m(gids)
     sel = np.flatnonzero(np.isin(m.rows, gids.astype(m.rows.dtype)))
     if sel.size > max_nnz:  # a hub row was drawn: keep whole rows up to the limit
         order = np.argsort(m.rows[sel], kind="stable")

@@ -276,3 +276,25 @@ def build_my_plan(m: CooMatrix, mesh: Mesh3D, rank: int, seed: int = 0, policy: 
     offsets, perm = bucket_blocks(m, directory.rowmap, directory.colmap, mesh)
     blk = extract_block(m, offsets, perm, mesh, x, y)
     return directory, build_rank_plan(blk, directory, (x, y, z), gnnz=m.nnz)
+
+
+def build_my_plan_from_spec(spec: str, mesh: Mesh3D, groups, seed: int = 0, policy: str = "respect_comm"):
+    """Plan of the calling rank for a synthetic matrix, with every rank generating only its own block where the
+    generator allows it (uniform, zipf, er): the 2D maps are functions of the seed, the block is generated in
+    place, and the touch masks are summed over the plane (the one collective of setup).  Other generators fall
+    back to building the whole matrix on every rank.  Returns (directory, plan, whole matrix or None)."""
+    from ..utils import generate
+    from .partition import directory_from_blocks, make_maps
+    rank = groups.rank if groups is not None else 0
+    x, y, z = mesh.coords_of(rank)
+    if groups is not None and mesh.size > 1:
+        probe = generate._spec_rowptr(spec, seed)
+        if probe is not None:
+            nrows, ncols = probe[0], probe[1]
+            rowmap, colmap = make_maps(nrows, ncols, mesh, seed)
+            block, gnnz = generate.block_from_spec(spec, seed, rowmap, x, colmap, y)
+            directory = directory_from_blocks(block, mesh, groups, seed, rowmap, colmap, policy)
+            return directory, build_rank_plan(block, directory, (x, y, z), gnnz=gnnz), None
+    m = generate.from_spec(spec, seed=seed)
+    directory, plan = build_my_plan(m, mesh, rank, seed=seed, policy=policy)
+    return directory, plan, m

@@ -96,6 +96,69 @@ def from_spec(spec: str, seed: int = 0) -> CooMatrix:
     raise ValueError(f"unknown generator spec {spec!r}")
 
 
+def _spec_rowptr(spec: str, seed: int):
+    """(nrows, ncols, rowptr, name) for the generators that draw every row independently (uniform, zipf, er);
+    None for the others (rmat removes duplicates globally, random draws positions globally)."""
+    kind, *args = spec.split(":")
+    h = native.host()
+    if kind == "uniform":
+        nrows, ncols, d = int(args[0]), int(args[1]), int(args[2])
+        deg = np.full(nrows, d, np.uint32)
+        name = f"uniform_{nrows}x{ncols}_d{d}"
+    elif kind == "zipf":
+        nrows, ncols = int(args[0]), int(args[1])
+        alpha = float(args[2]) if len(args) > 2 else 1.8
+        dmax = int(args[3]) if len(args) > 3 else 4096
+        deg = np.empty(nrows, np.uint32)
+        native.check(h.sp3_gen_degrees(nrows, 0, alpha, 1, min(dmax, ncols), seed, native.ptr(deg)), "zipf degrees")
+        name = f"zipf_{nrows}x{ncols}_a{alpha}"
+    elif kind == "er":
+        nrows, ncols, mean = int(args[0]), int(args[1]), float(args[2])
+        deg = np.empty(nrows, np.uint32)
+        native.check(h.sp3_gen_degrees(nrows, 1, mean, 0, ncols, seed, native.ptr(deg)), "poisson degrees")
+        name = f"er_{nrows}x{ncols}_d{mean:g}"
+    else:
+        return None
+    rowptr = np.zeros(nrows + 1, np.uint64)
+    np.cumsum(deg, out=rowptr[1:])
+    return nrows, ncols, rowptr, name
+
+
+def block_from_spec(spec: str, seed: int, rowmap=None, x: int = 0, colmap=None, y: int = 0):
+    """The part of the matrix `from_spec(spec, seed)` that lies in rows with rowmap == x and columns with
+    colmap == y (None keeps a whole side), generated directly: entry for entry the same positions and values as
+    in the whole matrix, without ever building it.  Returns (block with global ids, nonzeros of the whole
+    matrix), or None for generators that cannot be restricted (rmat, random).  This is what lets every rank
+    build only its own block of a synthetic matrix; the reference reads its chunk of a file instead
+    (src/parallel_io.hpp:81-127)."""
+    got = _spec_rowptr(spec, seed)
+    if got is None:
+        return None
+    nrows, ncols, rowptr, name = got
+    rm = None if rowmap is None else np.ascontiguousarray(rowmap, dtype=np.int32)
+    cm = None if colmap is None else np.ascontiguousarray(colmap, dtype=np.int32)
+    import ctypes
+    cnt = ctypes.c_uint64()
+    fn = native.host().sp3_gen_from_rowptr_block
+    native.check(fn(nrows, ncols, native.ptr(rowptr), seed, native.ptr(rm), x, native.ptr(cm), y,
+                    ctypes.addressof(cnt), None, None, None), f"{name} block count")
+    n = int(cnt.value)
+    rows, cols, vals = np.empty(n, np.uint32), np.empty(n, np.uint32), np.empty(n, np.float64)
+    native.check(fn(nrows, ncols, native.ptr(rowptr), seed, native.ptr(rm), x, native.ptr(cm), y,
+                    ctypes.addressof(cnt), native.ptr(rows), native.ptr(cols), native.ptr(vals)), f"{name} block")
+    return CooMatrix(nrows, ncols, rows, cols, vals, name=name), int(rowptr[-1])
+
+
+def rows_from_spec(spec: str, seed: int, row_ids):
+    """All entries of the given rows of `from_spec(spec, seed)` (the others are never generated), or None."""
+    got = _spec_rowptr(spec, seed)
+    if got is None:
+        return None
+    sel = np.ones(got[0], np.int32)
+    sel[np.asarray(row_ids, dtype=np.int64)] = 0
+    return block_from_spec(spec, seed, rowmap=sel, x=0)[0]
+
+
 FILL_NORMAL, FILL_GID_OVER_1000, FILL_CONST = 0, 1, 2
 
 

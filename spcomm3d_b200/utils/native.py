@@ -49,6 +49,7 @@ HOST_SIGS = {
     "sp3_gen_fixed_degree": ("int", "u64 u64 u32 u64 p p p"),
     "sp3_gen_degrees": ("int", "u64 int f64 u32 u32 u64 p"),
     "sp3_gen_from_rowptr": ("int", "u64 u64 p u64 p p p"),
+    "sp3_gen_from_rowptr_block": ("int", "u64 u64 p u64 p i32 p i32 p p p p"),
     "sp3_gen_rmat_keys": ("int", "u32 u64 f64 f64 f64 u64 p"),
     "sp3_sort_unique_u64": ("i64", "p u64"),
     "sp3_keys_to_coo": ("int", "p u64 u64 p p p"),

@@ -162,3 +162,30 @@ def _degenerate_rank(rank, world, which):
 def test_degenerate_matrices_distributed(which):
     """No nonzeros, a 1 x 1 matrix, fewer rows than ranks: most blocks and exchanges are empty."""
     run_ranks(_degenerate_rank, 4, which)
+
+
+def _plan_from_own_block(rank, world, meshstr, spec):
+    """Every rank generates only its own block of a synthetic matrix; the plan must equal the one built from
+    the whole matrix, array for array."""
+    from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups
+    from spcomm3d_b200.parallel.plan import build_my_plan, build_my_plan_from_spec
+    from spcomm3d_b200.utils import generate
+    mesh = Mesh3D.parse(meshstr)
+    groups = MeshGroups.create(mesh)
+    _, plan, whole = build_my_plan_from_spec(spec, mesh, groups, seed=7)
+    assert whole is None   # the whole matrix was never built
+    m = generate.from_spec(spec, seed=7)
+    _, ref = build_my_plan(m, mesh, rank, seed=7)
+    assert plan.gnnz == ref.gnnz == m.nnz and plan.coords == ref.coords
+    for name in ("rowptr", "rowidx", "colidx", "vals"):
+        assert np.array_equal(getattr(plan, name), getattr(ref, name)), name
+    for side in ("row", "col"):
+        for f in ("owned_gids", "local_gids", "recv_counts", "recv_src_idx", "recv_peer", "send_counts", "send_idx",
+                  "peer_owned", "push_offset"):
+            assert np.array_equal(getattr(getattr(plan, side), f), getattr(getattr(ref, side), f)), (side, f)
+
+
+@pytest.mark.parametrize("meshstr,spec", [("2x2x1", "er:500:400:5"), ("2x1x2", "zipf:600:800:1.6:200"),
+                                          ("1x2x2", "uniform:300:300:4")])
+def test_plan_from_own_block_equals_plan_from_whole_matrix(meshstr, spec):
+    run_ranks(_plan_from_own_block, 4, meshstr, spec)
