@@ -199,6 +199,11 @@ def build_tools(force=False, verbose=False) -> Path:
     srcs = [CSRC / "tools" / "conv2bin.cpp", CSRC / "host" / "io.cpp"]
     cmd = ["g++", "-std=c++17", "-O3", f"-I{CSRC / 'host'}"]
     _build(exe, srcs, _sources("host", {".hpp"}), cmd, force, verbose)
+    # row-gather throughput probe (vector loads against bulk copies), see its header
+    gb = LIBDIR / "gather_bench"
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    _build(gb, [CSRC / "tools" / "gather_bench.cu"], [CSRC / "kernels" / "sp3_async.cuh", CSRC / "kernels" / "sp3_cuda.cuh"],
+           [nvcc, "-std=c++17", "-O3", "-lineinfo", *NVCC_ARCH, f"-I{CSRC / 'kernels'}"], force, verbose)
     return exe
 
 
