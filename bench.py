@@ -256,9 +256,11 @@ def run_ours(args):
         step.run_device()
     barrier()
     agree_healthy("after warm-up")
-    launches0 = cuda_ops.LAUNCHES
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
-    with ClockSampler(dev_index) as clocks:
+    sampler = ClockSampler(dev_index)   # NVML start-up happens here, before the barrier that opens the timed region
+    with sampler as clocks:
+        barrier()                       # every rank enters the timed region together
+        launches0 = cuda_ops.LAUNCHES
         ev[0].record()
         for i in range(args.steps):
             step.sddmm.run_async()

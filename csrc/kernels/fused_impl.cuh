@@ -63,7 +63,6 @@ enum Ctrl : int { C_TICKET_MAIN = 0, C_PULLS_DONE = 1, C_MAIN_DONE = 2, C_TICKET
 enum Phase : int { PH_START = 1, PH_MAIN = 2, PH_FINISH = 4 };
 enum WaitSite : int { W_READY = 1, W_PULLS = 2, W_PART = 3, W_DONE = 4, W_WORK = 5 };
 
-constexpr int PULL_ROWS = 64;      // dense rows per pull ticket
 constexpr int REDUCE_ELEMS = 2048; // values per SDDMM reduce ticket
 constexpr int PUSH_ELEMS = 4096;   // partial values per SDDMM push ticket
 constexpr int REDUCE_ROWS = 32;    // owned rows per SpMM reduce ticket
@@ -197,14 +196,38 @@ __device__ __forceinline__ void pull_rows(int r0, int r1, const float4* const* _
 // store into the local block (the rows of a tile are consecutive there).  Nothing passes through registers and
 // the warp never stalls on a load, so a few warps keep NVLink busy while all the others compute.
 constexpr int BULK_STAGES = 3;
-constexpr unsigned BULK_STAGE_BYTES = 4096;   // 3 x 4 KB per block: two stages in flight per puller, 49 KB of an SM's
-                                               // shared memory with four resident blocks (the rest stays L1 cache)
-constexpr unsigned BULK_SMEM_BYTES = BULK_STAGES * BULK_STAGE_BYTES + 64;
+constexpr int BULK_MAX_PULLERS = 4;   // puller warps per block
+
+// Pull set-up of a launch (host side -> kernel): how many warps of every block pull with bulk copies (0: vector
+// loads), the bytes of one ring stage and the dense rows of one pull ticket.
+struct PullConfig {
+    int pullers;
+    unsigned stage_bytes;
+    int tile_rows;
+};
+inline size_t bulk_smem_bytes(const PullConfig& pc) {
+    return pc.pullers > 0 ? (size_t)pc.pullers * BULK_STAGES * (pc.stage_bytes + 8) + 64 : 0;
+}
 
 struct BulkRing {
-    unsigned ring, bars;    // shared-memory addresses of the stages and of their mbarriers
+    unsigned ring, bars;    // shared-memory addresses of this warp's stages and of their mbarriers
+    unsigned stage_bytes;
     unsigned long long g;   // chunks this warp has issued so far: stage g % BULK_STAGES, phase parity (g / BULK_STAGES) & 1
 };
+
+// Ring of puller warp `w` of this block inside the dynamic shared memory; warp w initialises its own barriers.
+__device__ __forceinline__ BulkRing bulk_ring_init(unsigned char* dyn_smem, const PullConfig& pc, int warp, int lane) {
+    BulkRing br{0u, 0u, pc.stage_bytes, 0ull};
+    if (pc.pullers <= 0) return br;
+    const unsigned base = smem_u32(dyn_smem);
+    br.ring = base + (unsigned)warp * BULK_STAGES * pc.stage_bytes;
+    br.bars = base + (unsigned)pc.pullers * BULK_STAGES * pc.stage_bytes + (unsigned)warp * BULK_STAGES * 8u;
+    if (warp < pc.pullers && lane == 0) {
+        for (int st = 0; st < BULK_STAGES; ++st) mbar_init(br.bars + 8u * st, 1);
+        mbar_init_fence();
+    }
+    return br;
+}
 
 // Copies rows [r0, r1) of a receive list into dst (row r lands at dst + r * nvec vectors; the local block has
 // no padding between rows).  All lanes of one warp call it.  Returns false when a load did not arrive in time
@@ -214,8 +237,8 @@ __device__ __forceinline__ bool bulk_pull_tile(BulkRing& br, const FusedComm& c,
                                                const float4* const* __restrict__ src, float4* __restrict__ dst,
                                                int nvec, int lane) {
     const unsigned row_bytes = (unsigned)nvec * 16u;
-    int rps = (int)(BULK_STAGE_BYTES / row_bytes);   // rows per stage
-    rps = rps > PULL_ROWS ? PULL_ROWS : (rps < 1 ? 1 : rps);
+    int rps = (int)(br.stage_bytes / row_bytes);   // rows per stage
+    rps = rps < 1 ? 1 : rps;
     const int n = r1 - r0, nch = (n + rps - 1) / rps;
     bool ok = true;
     for (int ch = 0; ch < nch + BULK_STAGES - 1; ++ch) {
@@ -228,7 +251,7 @@ __device__ __forceinline__ bool bulk_pull_tile(BulkRing& br, const FusedComm& c,
             if (lane == 0) mbar_expect_tx(br.bars + 8u * st, (unsigned)cn * row_bytes);
             __syncwarp();
             for (int i = lane; i < cn; i += 32)
-                bulk_load(br.ring + st * BULK_STAGE_BYTES + (unsigned)i * row_bytes, ldg_ptr(src + r0 + c0 + i),
+                bulk_load(br.ring + st * br.stage_bytes + (unsigned)i * row_bytes, ldg_ptr(src + r0 + c0 + i),
                           row_bytes, br.bars + 8u * st);
         }
         const int pc = ch - (BULK_STAGES - 1);
@@ -244,7 +267,7 @@ __device__ __forceinline__ bool bulk_pull_tile(BulkRing& br, const FusedComm& c,
             if (ok) {
                 const int c0 = pc * rps, cn = n - c0 < rps ? n - c0 : rps;
                 if (lane == 0) {
-                    bulk_store(dst + (long long)(r0 + c0) * nvec, br.ring + st * BULK_STAGE_BYTES, (unsigned)cn * row_bytes);
+                    bulk_store(dst + (long long)(r0 + c0) * nvec, br.ring + st * br.stage_bytes, (unsigned)cn * row_bytes);
                     bulk_commit();
                 }
             }
@@ -351,7 +374,7 @@ struct FusedSddmmArgs {
     const int* pull_order;
     int n_waves, tiles_per_wave;
     const long long* wave_nnz;
-    int bulk_pull;                // 1: the first warp of every block pulls with bulk copies (see bulk_pull_tile)
+    PullConfig pull;              // who pulls, and in which portions (see PullConfig, bulk_pull_tile)
 };
 
 #if SP3_FUSED_IS_F32
@@ -420,18 +443,11 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
     __shared__ unsigned long long a_bases[MAX_RANKS];
-    extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: BULK_SMEM_BYTES, else nothing
+    extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: the pullers' rings, else nothing
     if (threadIdx.x < MAX_RANKS) a_bases[threadIdx.x] = threadIdx.x < a.world ? a.a_bases[threadIdx.x] : 0ull;
-    const bool bulk = a.bulk_pull != 0;
-    BulkRing br{0u, 0u, 0ull};
-    if (bulk) {
-        br.ring = smem_u32(dyn_smem);
-        br.bars = br.ring + BULK_STAGES * BULK_STAGE_BYTES;
-        if (threadIdx.x == 0) {
-            for (int st = 0; st < BULK_STAGES; ++st) mbar_init(br.bars + 8u * st, 1);
-            mbar_init_fence();
-        }
-    }
+    const bool bulk = a.pull.pullers > 0;
+    const int PULL_ROWS = a.pull.tile_rows;
+    BulkRing br = bulk_ring_init(dyn_smem, a.pull, threadIdx.x >> 5, lane);
     __syncthreads();
     if (c.phases & PH_START) start_phase(c);
     if (c.phases & PH_MAIN) {
@@ -455,7 +471,7 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
         // pullers: in bulk mode the first warp of every block and nobody else; otherwise one warp in four,
         // helped by any warp whose own units are not ready yet
-        const bool is_puller = bulk ? threadIdx.x < 32 : (gwarp & 3) == 0;
+        const bool is_puller = bulk ? (int)(threadIdx.x >> 5) < a.pull.pullers : (gwarp & 3) == 0;
         bool pulls_left = n_pull > 0 && (!bulk || is_puller);
         const long long n_free_units = a.nnz_free / per_unit;  // units that touch no pulled row
         const int n_waves = n_pull > 0 ? (a.n_waves > 0 ? a.n_waves : 1) : 0;
@@ -663,7 +679,13 @@ struct FusedSpmmArgs {
     int atomic;
     int red_v4;                   // 1: 16-byte vector atomics also for remote rows, 0: one 4-byte atomic per value
     const unsigned char* crow_flag;  // [n_owned_y] 1: row receives contributions from peers
-    int bulk_pull;                // 1: the first warp of every block pulls the X rows with bulk copies
+    PullConfig pull;              // who pulls, and in which portions
+    // Pull waves, as in the SDDMM kernel: the work items are given sorted by the last wave that brings one of
+    // their X rows (class 0: all columns owned); wave_items[c] = items that can run once the first c waves are
+    // complete.  Long rows are cut into pieces at class boundaries (their nonzeros are sorted by class), so the
+    // owned part of a hub row is computed while the pulls are in flight.
+    int n_waves, tiles_per_wave;
+    const int* wave_items;
 };
 
 // Rows I own go straight into the result (Y = beta*Y + my partial; the owners' FINISH phase then adds what
@@ -712,18 +734,11 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
     const int lane = threadIdx.x & 31;
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
-    extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: BULK_SMEM_BYTES, else nothing
-    const bool bulk = a.bulk_pull != 0;
-    BulkRing br{0u, 0u, 0ull};
-    if (bulk) {
-        br.ring = smem_u32(dyn_smem);
-        br.bars = br.ring + BULK_STAGES * BULK_STAGE_BYTES;
-        if (threadIdx.x == 0) {
-            for (int st = 0; st < BULK_STAGES; ++st) mbar_init(br.bars + 8u * st, 1);
-            mbar_init_fence();
-        }
-        __syncthreads();
-    }
+    extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: the pullers' rings, else nothing
+    const bool bulk = a.pull.pullers > 0;
+    const int PULL_ROWS = a.pull.tile_rows;
+    BulkRing br = bulk_ring_init(dyn_smem, a.pull, threadIdx.x >> 5, lane);
+    __syncthreads();
     if ((c.phases & PH_START) && !ATOMIC) start_phase(c);
     if ((c.phases & PH_START) && ATOMIC) {
         // scale the rows that peers will add to, then tell readers and contributors that this rank is ready
@@ -765,29 +780,55 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
         const long long ldx_v = a.ldx / VN;
         const EmitOwnedOrPush emit{reinterpret_cast<vec*>(a.Y), a.ldy / VN, (real)a.beta, a.n_owned_y, a.y_dst,
                                    parity ? a.parity_off_v : 0};
-        bool pulled = n_pull == 0;
-        // bulk mode: the first warp of every block pulls with the asynchronous copy unit; otherwise all warps pull
-        while (ok && (!bulk || threadIdx.x < 32) && !aborted(c)) {
+        // Pullers: in bulk mode the first warps of every block; with vector loads one warp in four, helped by any
+        // warp whose own items are not ready yet.  The others start on the items that need no pulled row.
+        const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+        const bool is_puller = bulk ? (int)(threadIdx.x >> 5) < a.pull.pullers : (gwarp & 3) == 0;
+        bool pulls_left = n_pull > 0 && (!bulk || is_puller);
+        const int n_waves = n_pull > 0 ? (a.n_waves > 0 ? a.n_waves : 1) : 0;
+        const int tpw = a.n_waves > 0 ? a.tiles_per_wave : (n_pull > 0 ? n_pull : 1);
+        auto pull_one = [&]() -> bool {
             const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
-            if (t >= n_pull) break;
+            if (t >= n_pull) return false;
             const int r0 = t * PULL_ROWS;
             const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
-            if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, a.x_src, reinterpret_cast<float4*>(Xv + (long long)a.n_owned_x * ldx_v), a.nvec, lane)) break; }
-            else pull_rows(r0, r1, a.x_src, reinterpret_cast<float4*>(Xv + (long long)a.n_owned_x * ldx_v), ldx_v, a.nvec, lane);
+            float4* dst = reinterpret_cast<float4*>(Xv + (long long)a.n_owned_x * ldx_v);
+            if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, a.x_src, dst, a.nvec, lane)) return false; }
+            else pull_rows(r0, r1, a.x_src, dst, ldx_v, a.nvec, lane);
             __threadfence();
             __syncwarp();
-            if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
-        }
+            if (lane == 0) {
+                atomicAdd(c.ctrl + C_WAVE0 + t / tpw, 1);
+                if (atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
+            }
+            return true;
+        };
+        // items runnable once the first w waves are complete (without wave data: none before the last pull)
+        auto items_after = [&](int w) -> int {
+            if (w >= n_waves) return a.nitems;
+            return a.wave_items ? __ldg(a.wave_items + w) : 0;
+        };
+        int waves_ready = 0;
+        auto ensure_waves = [&](int i1) -> bool {
+            while (waves_ready < n_waves && i1 > items_after(waves_ready)) {
+                const int w = waves_ready;
+                const int want = (w + 1) * tpw <= n_pull ? tpw : n_pull - w * tpw;
+                if (ld_acquire_gpu(c.ctrl + C_WAVE0 + w) >= want) { ++waves_ready; continue; }
+                if (pulls_left) { pulls_left = pull_one(); continue; }
+                if (!wait_counter(c, C_WAVE0 + w, want, W_PULLS)) return false;
+                ++waves_ready;
+            }
+            return true;
+        };
+        if (is_puller)
+            while (ok && pulls_left && !aborted(c)) pulls_left = pull_one();
         const int SPMM_ITEMS_PER_TICKET = per_ticket(a.nitems, nwarps, SPMM_ITEMS_PER_TICKET_MAX);
         while (ok) {
             const int i0 = warp_ticket(c.ctrl + C_TICKET_WORK, lane, SPMM_ITEMS_PER_TICKET);
             if (i0 >= a.nitems) break;
-            if (!pulled) {
-                ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
-                pulled = true;
-                if (!ok) break;
-            }
             const int i1 = i0 + SPMM_ITEMS_PER_TICKET < a.nitems ? i0 + SPMM_ITEMS_PER_TICKET : a.nitems;
+            ok = ensure_waves(i1);
+            if (!ok) break;
             if constexpr (ATOMIC) {
                 const EmitOwnedOrAdd add{reinterpret_cast<vec*>(a.Y), a.ldy / VN, (real)a.beta, a.n_owned_y, a.y_dst,
                                          a.crow_flag, a.red_v4};
@@ -800,6 +841,7 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
                                                                            Xv, ldx_v, a.nvec, emit, a.lg, lane);
             }
         }
+        while (ok && pulls_left) pulls_left = pull_one();  // no item left but tiles remain (tiny blocks)
         main_epilogue(c, lane, nwarps);
     }
     if (c.phases & PH_FINISH) {
@@ -878,7 +920,14 @@ template <typename K, typename A>
 static int launch_resident(K kernel, const A& args, cudaStream_t st) {
     A copy = args;
     void* params[] = {&copy};
-    const size_t smem = args.bulk_pull ? BULK_SMEM_BYTES : 0;
+    if (args.pull.pullers < 0 || args.pull.pullers > BULK_MAX_PULLERS || args.pull.tile_rows < 1 ||
+        (args.pull.pullers > 0 && (args.pull.stage_bytes < 1024 || args.pull.stage_bytes % 16)))
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = bulk_smem_bytes(args.pull);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
     const unsigned blocks = persistent_blocks(kernel, 0, 256, smem);
     return (int)cudaLaunchCooperativeKernel((const void*)kernel, dim3(blocks), dim3(256), params, smem, st);
 }
@@ -906,6 +955,7 @@ SP3_API int SP3_FUSED_CAT(sp3_fused_sddmm_, SP3_FUSED_SUFFIX)(const void* args, 
 SP3_API int SP3_FUSED_CAT(sp3_fused_spmm_, SP3_FUSED_SUFFIX)(const void* args, void* stream) {
     FusedSpmmArgs a = *reinterpret_cast<const FusedSpmmArgs*>(args);
     cudaStream_t st = (cudaStream_t)stream;
+    if (a.n_waves > MAX_WAVES) return (int)cudaErrorInvalidValue;
     cudaError_t e = cudaMemsetAsync(a.comm.ctrl, 0, C_WORDS * sizeof(int), st);
     if (e != cudaSuccess) return (int)e;
     int G, R, rc = 0;

@@ -193,13 +193,15 @@ __device__ __forceinline__ void sddmm_warp_unit(long long unit, long long nnz, c
 // ---------------------------------------------------------------------------
 // SpMM
 // ---------------------------------------------------------------------------
+constexpr int SPMM_PIECE_SHIFT = 20;   // at most 2^20 split rows, 2^11 pieces per row
+
 struct SpmmLong {
     const int* first_piece;  // [nlong] first carry slot of each long row
     const int* npieces;      // [nlong]
     int* counters;           // [nlong] zero at launch; reset by the finishing warp
     void* carry;             // [total pieces, ldc] scratch
     long long ldc;           // elements per carry row
-    int piece_len;           // nonzeros per piece
+    int piece_len;           // largest number of nonzeros of a piece
     int* ticket;             // optional work counter (zero at launch): items are then handed out dynamically
 };
 
@@ -365,9 +367,10 @@ __device__ __forceinline__ void spmm_warp_item(const int4 item, const long long*
     for (int m = G; m < 32; m <<= 1)
 #pragma unroll
         for (int r = 0; r < R; ++r) vadd(acc[r], shfl_xor_vec(acc[r], m));
-    const int lr = item.w, row = item.x;
+    // item.w = long-row slot | number of this piece inside its row << SPMM_PIECE_SHIFT
+    const int lr = item.w & ((1 << SPMM_PIECE_SHIFT) - 1), row = item.x;
     const int first = __ldg(lg.first_piece + lr), np = __ldg(lg.npieces + lr);
-    const int piece = first + (int)((item.y - rowptr[row]) / lg.piece_len);
+    const int piece = first + (item.w >> SPMM_PIECE_SHIFT);
     V* carry = reinterpret_cast<V*>(lg.carry);
     const long long ldc_v = lg.ldc / Vec<T>::N;
     if (slot == 0)

@@ -35,20 +35,28 @@ def main(argv=None):
     ap.add_argument("--meshes", default=None, help="comma list of XxYxZ (default: the mesh given by -c)")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--chain", action="store_true",
+                    help="also time the attention-style chain Y = (S o (A B^T)) X (SDDMM scores as SpMM values)")
     args = ap.parse_args(argv)
     rt = Runtime(args)
     import torch.distributed as dist
-    m = generate.from_spec(args.gen, seed=args.seed) if args.gen else None
-    if m is None:
+    from ..parallel.plan import build_my_plan_from_spec
+    m = None
+    if not args.gen:
         from ..utils import binfmt
         m = binfmt.read_mtx(args.matrix) if args.matrix.endswith(".mtx") else binfmt.read_bin(args.matrix)
+    elif rt.world == 1 or generate._spec_rowptr(args.gen, args.seed) is None:
+        m = generate.from_spec(args.gen, seed=args.seed)   # generators that cannot be restricted to a block
     meshes = [Mesh3D.parse(t) for t in args.meshes.split(",")] if args.meshes else [rt.mesh]
     for mesh in meshes:
         if mesh.size != rt.world:
             rt.say(f"# skipping mesh {mesh}: needs {mesh.size} ranks")
             continue
         groups = MeshGroups.create(mesh) if rt.world > 1 else None
-        _, plan = build_my_plan(m, mesh, rt.rank, seed=args.seed, policy=args.policy)
+        if m is not None:
+            _, plan = build_my_plan(m, mesh, rt.rank, seed=args.seed, policy=args.policy)
+        else:   # every rank generates its own block only
+            _, plan, _ = build_my_plan_from_spec(args.gen, mesh, groups, seed=args.seed, policy=args.policy)
         for k in klist(args.klist):
             for variant in rt.variants(args, ("fused", "sparseNRB", "dense")):
                 for cls in (DistSDDMM, DistSpMM):
@@ -110,6 +118,41 @@ def main(argv=None):
                     rt.say(json.dumps(rec))
                     op.close()   # collective: status check, multicast binding dropped by all ranks together
                     del op
+                if args.chain and variant in ("fused", "sparseNRB", "sparse"):
+                    from ..models.layer import GatLayer
+                    layer = GatLayer(plan, groups, k, rt.dtype, rt.device, variant)
+                    layer.sddmm.fill_owned(layer.sddmm.A_owned, plan.row.owned_gids, seed=args.seed, stream=1)
+                    layer.sddmm.fill_owned(layer.sddmm.B_owned, plan.col.owned_gids, seed=args.seed, stream=2)
+                    layer.spmm.fill_owned(layer.spmm.X_owned, plan.col.owned_gids, seed=args.seed, stream=2)
+                    for op_ in (layer.sddmm, layer.spmm):
+                        op_.timer.enabled = False
+                    for _ in range(args.warmup):
+                        layer.run()
+                    rt.barrier()
+                    if rt.device.type == "cuda":
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record()
+                    else:
+                        import time
+                        t0 = time.perf_counter()
+                    for _ in range(args.steps):
+                        layer.run()
+                    if rt.device.type == "cuda":
+                        b.record()
+                        rt.barrier()
+                        ms = a.elapsed_time(b) / args.steps
+                    else:
+                        rt.barrier()
+                        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+                    t = torch.tensor([ms], dtype=torch.float64, device=rt.device)
+                    if rt.world > 1:
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    rt.say(json.dumps({"kernel": "sddmm->spmm chain", "mesh": str(mesh), "variant": variant, "k": k,
+                                       "matrix": plan.name, "ms": round(float(t), 4),
+                                       "gflops": round(2 * layer.sddmm.flops() / float(t) / 1e6, 1)}))
+                    layer.sddmm.close()
+                    layer.spmm.close()
+                    del layer
     rt.finish()
 
 

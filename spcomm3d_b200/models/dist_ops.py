@@ -279,7 +279,8 @@ class DistSpMM(_Dist3DOp):
         if variant == "fused":
             from ..ops.fused import FusedSpMM
             self._fused = FusedSpMM(self, **{k_: v for k_, v in kw.items()
-                                             if k_ in ("heap", "fabric", "timeout_s", "reduce", "red_v4", "bulk_pull")})
+                                             if k_ in ("heap", "fabric", "timeout_s", "reduce", "red_v4", "bulk_pull",
+                                                       "overlap")})
             self.X_loc, self.Y_loc = self._fused.X_loc, self._fused.Y_loc
         else:
             self.X_loc, self.Y_loc = self._alloc_local(p.col), self._alloc_local(p.row)
@@ -329,6 +330,13 @@ class DistSpMM(_Dist3DOp):
 
     def _local_buffers(self):
         return [(self.X_loc, self.plan.col)]
+
+    def values_changed(self):
+        """Tell the op that `vals` (the values of S, CSR order) was written to: the fused kernel keeps a
+        re-ordered copy.  The library variants read `vals` directly."""
+        f = getattr(self, "_fused", None)
+        if f is not None:
+            f.refresh_values()
 
     def run(self, beta: float = 0.0) -> torch.Tensor:
         """One distributed SpMM: Y_owned = beta*Y_owned + (S X)[owned rows]."""

@@ -206,4 +206,5 @@ class GatLayer:
                     self.spmm.vals[o:o + l].copy_(self._all[z, :l])
                 else:
                     self.spmm.vals.index_copy_(0, self._pos[o:o + l], self._all[z, :l])
+        self.spmm.values_changed()
         return self.spmm.run()

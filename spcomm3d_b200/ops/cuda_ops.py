@@ -22,6 +22,9 @@ ITEM_NNZ = int(os.environ.get("SP3_ITEM_NNZ", 128))
 ITEM_ROWS = int(os.environ.get("SP3_ITEM_ROWS", 64))
 
 
+PIECE_SHIFT = 20   # SPMM_PIECE_SHIFT of csrc/kernels/sp3_kernels.cuh
+
+
 def _stream():
     return torch.cuda.current_stream().cuda_stream
 
@@ -75,7 +78,7 @@ def build_spmm_items(rowptr: np.ndarray, long_row: int | None = None, item_nnz: 
 
     Returns (items int32[n,4], first_piece int32[nlong], npieces int32[nlong]).
     rows item  = (row_begin, row_end, 0, -1)
-    piece item = (row, nnz_begin, nnz_end, long_row_slot)
+    piece item = (row, nnz_begin, nnz_end, long_row_slot | piece_number_in_row << PIECE_SHIFT)
     """
     long_row = LONG_ROW if long_row is None else long_row
     item_nnz = ITEM_NNZ if item_nnz is None else item_nnz
@@ -101,7 +104,9 @@ def build_spmm_items(rowptr: np.ndarray, long_row: int | None = None, item_nnz: 
         r = long_rows[slot]
         b = rowptr[r] + j * long_row
         e = np.minimum(b + long_row, rowptr[r + 1])
-        piece_items = np.stack([r, b, e, slot], axis=1)
+        if long_rows.size >= 1 << PIECE_SHIFT or int(npieces.max()) >= 1 << (31 - PIECE_SHIFT):
+            raise ValueError("too many split rows or pieces per row for the item encoding")
+        piece_items = np.stack([r, b, e, slot + (j << PIECE_SHIFT)], axis=1)
         items = np.concatenate([piece_items, rows_items])  # heavy work first
     else:
         items = rows_items
@@ -110,13 +115,83 @@ def build_spmm_items(rowptr: np.ndarray, long_row: int | None = None, item_nnz: 
     return items.astype(np.int32), first.astype(np.int32), npieces.astype(np.int32)
 
 
+def build_spmm_wave_items(rowptr: np.ndarray, cls: np.ndarray, n_classes: int, long_row: int | None = None,
+                          item_nnz: int | None = None, item_rows: int | None = None):
+    """Work items for an SpMM whose column-side rows arrive in waves.  `cls[q]` is the class of nonzero q
+    (0: its dense row is there from the start; c: it arrives with wave c - 1).
+
+    Long rows have their nonzeros sorted by class (stable) and are cut into pieces at class boundaries (and
+    every `long_row` nonzeros), so that the part of a hub row whose columns are already there is computable at
+    once; other rows are grouped as in `build_spmm_items` and take the largest class of their nonzeros.  Items
+    are returned sorted by class.
+
+    Returns (perm int64[nnz]: source position of every nonzero of the re-ordered CSR arrays, items, first_piece,
+    npieces, class_items int32[n_classes]: number of items of classes 0..c)."""
+    long_row = LONG_ROW if long_row is None else long_row
+    nnz = int(rowptr[-1])
+    deg = np.diff(rowptr)
+    std_items, _, _ = build_spmm_items(rowptr, long_row, item_nnz, item_rows)
+    rows_items = std_items[std_items[:, 3] < 0].astype(np.int64)
+    perm = np.arange(nnz, dtype=np.int64)
+    lrows = np.flatnonzero(deg > long_row)
+    pieces = np.zeros((0, 4), np.int64)
+    pcls = np.zeros(0, np.int64)
+    first = np.zeros(0, np.int64)
+    npieces = np.zeros(0, np.int64)
+    if lrows.size:
+        ldeg = deg[lrows]
+        starts = np.repeat(rowptr[lrows], ldeg)
+        slot_of = np.repeat(np.arange(lrows.size), ldeg)
+        within = np.arange(int(ldeg.sum())) - np.repeat(np.cumsum(ldeg) - ldeg, ldeg)
+        idx = starts + within                                  # nonzeros of the long rows, ascending
+        order = np.argsort(slot_of * 256 + cls[idx].astype(np.int64), kind="stable")
+        perm[idx] = idx[order]
+        c_sorted = cls[idx[order]].astype(np.int64)
+        # runs of equal (row, class), cut every long_row nonzeros
+        key = slot_of * 256 + c_sorted                         # slot_of is already grouped by row
+        run_start = np.flatnonzero(np.concatenate([[True], key[1:] != key[:-1]]))
+        run_len = np.diff(np.append(run_start, key.size))
+        nchunk = (run_len + long_row - 1) // long_row
+        chunk_run = np.repeat(np.arange(run_start.size), nchunk)
+        chunk_j = np.arange(int(nchunk.sum())) - np.repeat(np.cumsum(nchunk) - nchunk, nchunk)
+        b_rel = run_start[chunk_run] + chunk_j * long_row
+        e_rel = np.minimum(b_rel + long_row, run_start[chunk_run] + run_len[chunk_run])
+        p_slot = slot_of[b_rel]
+        npieces = np.bincount(p_slot, minlength=lrows.size)
+        first = np.cumsum(npieces) - npieces
+        p_num = np.arange(p_slot.size) - first[p_slot]
+        if lrows.size >= 1 << PIECE_SHIFT or int(npieces.max()) >= 1 << (31 - PIECE_SHIFT):
+            raise ValueError("too many split rows or pieces per row for the item encoding")
+        pieces = np.stack([lrows[p_slot], idx[b_rel], idx[b_rel] + (e_rel - b_rel), p_slot + (p_num << PIECE_SHIFT)], axis=1)
+        pcls = c_sorted[b_rel]
+    # class of a rows item: the largest class among its nonzeros
+    rcls = np.zeros(rows_items.shape[0], np.int64)
+    if rows_items.shape[0] and nnz:
+        b, e = rowptr[rows_items[:, 0]], rowptr[rows_items[:, 1]]
+        nonempty = e > b
+        if nonempty.any():
+            cmax = np.maximum.reduceat(np.append(cls, 0).astype(np.int64), np.stack([b[nonempty], e[nonempty]], 1).ravel())[::2]
+            rcls[nonempty] = cmax
+    items = np.concatenate([pieces, rows_items])
+    icls = np.concatenate([pcls, rcls])
+    order = np.argsort(icls, kind="stable")                    # pieces stay ahead of rows items inside a class
+    items = items[order]
+    class_items = np.cumsum(np.bincount(icls, minlength=n_classes))[:n_classes]
+    if items.size and items.max() >= 2 ** 31:
+        raise ValueError("more than 2^31 nonzeros or rows on one rank")
+    return perm, items.astype(np.int32), first.astype(np.int32), npieces.astype(np.int32), class_items.astype(np.int32)
+
+
 class SpmmSchedule:
     """Device-resident SpMM work items plus the scratch the long-row path
     needs: one carry row per piece and one counter per long row."""
 
-    def __init__(self, rowptr: torch.Tensor, k_max: int = 0, dtype=torch.float32, **kw):
-        rp = rowptr.cpu().numpy()
-        items, first, npieces = build_spmm_items(rp, **kw)
+    def __init__(self, rowptr: torch.Tensor, k_max: int = 0, dtype=torch.float32, arrays=None, **kw):
+        if arrays is None:
+            rp = rowptr.cpu().numpy()
+            items, first, npieces = build_spmm_items(rp, **kw)
+        else:   # (items, first_piece, npieces) built elsewhere, e.g. by build_spmm_wave_items
+            items, first, npieces = arrays
         dev = rowptr.device
         self.piece_len = kw.get("long_row", LONG_ROW)
         self.items = torch.from_numpy(items).to(dev).contiguous()

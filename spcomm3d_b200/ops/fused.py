@@ -23,8 +23,7 @@ from ..utils import native
 from . import cuda_ops
 
 MAX_RANKS = 64
-MAX_WAVES = 32   # pull waves a kernel can track (csrc/kernels/fused_ops.cu)
-PULL_ROWS = 64   # dense rows per pull tile
+MAX_WAVES = 32   # pull waves a kernel can track (csrc/kernels/fused_impl.cuh)
 F_KINDS = 3
 PH_START, PH_MAIN, PH_FINISH = 1, 2, 4
 PH_ALL = 7
@@ -41,6 +40,10 @@ class _Comm(C.Structure):
                 ("n_push", C.c_int), ("n_contrib", C.c_int), ("stamps", P)]
 
 
+class _PullConfig(C.Structure):
+    _fields_ = [("pullers", C.c_int), ("stage_bytes", C.c_uint), ("tile_rows", C.c_int)]
+
+
 class _SddmmArgs(C.Structure):
     _fields_ = [("comm", _Comm), ("nnz", C.c_longlong), ("rowidx", P), ("colidx", P), ("sval", P),
                 ("a_refs", P), ("a_bases", P), ("world", C.c_int), ("B_loc", P), ("ldb", C.c_longlong), ("n_owned_b", C.c_int),
@@ -49,7 +52,7 @@ class _SddmmArgs(C.Structure):
                 ("part", P), ("direct_push", C.c_int), ("orig", P), ("nnz_free", C.c_longlong), ("work_per_pull", C.c_int),
                 ("n_recv_a", C.c_int), ("a_src", P), ("A_stage", P), ("mc_part", P), ("part_stride", C.c_longlong),
                 ("pull_order", P), ("n_waves", C.c_int), ("tiles_per_wave", C.c_int), ("wave_nnz", P),
-                ("bulk_pull", C.c_int)]
+                ("pull", _PullConfig)]
 
 
 class _SpmmLong(C.Structure):
@@ -64,7 +67,7 @@ class _SpmmArgs(C.Structure):
                 ("crows", P), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
                 ("ldy", C.c_longlong), ("beta", C.c_double), ("cptr", P), ("cslot", P), ("slots", P),
                 ("lds", C.c_longlong), ("atomic", C.c_int), ("red_v4", C.c_int), ("crow_flag", P),
-                ("bulk_pull", C.c_int)]
+                ("pull", _PullConfig), ("n_waves", C.c_int), ("tiles_per_wave", C.c_int), ("wave_items", P)]
 
 
 _checked_layout = False
@@ -152,6 +155,20 @@ class _FusedBase:
 
     def region_sizes_for(self, plan, k_loc):
         return self.region_sizes(plan, k_loc, dtype=self.dtype)
+
+    def _pull_config(self, cfg: _PullConfig):
+        """Pull set-up of this op: bulk mode = `SP3_FUSED_PULLERS` warps per block (default 1) with ring stages
+        of `SP3_FUSED_STAGE_BYTES` (default 8 KB) and pull tickets of about 64 KB; vector-load mode = tickets
+        of 64 rows."""
+        if self.bulk_pull:
+            cfg.pullers = max(1, min(4, int(os.environ.get("SP3_FUSED_PULLERS", "1"))))
+            stage = int(os.environ.get("SP3_FUSED_STAGE_BYTES", "8192")) // 16 * 16
+            cfg.stage_bytes = max(stage, self.row_bytes, 1024)
+            tile_bytes = int(os.environ.get("SP3_FUSED_TILE_BYTES", "65536"))
+            cfg.tile_rows = max(16, min(1024, tile_bytes // self.row_bytes))
+        else:
+            cfg.pullers, cfg.stage_bytes, cfg.tile_rows = 0, 0, 64
+        self.tile_rows = int(cfg.tile_rows)
 
     def _fn(self, kernel: str):
         return getattr(native.cuda(), f"sp3_fused_{kernel}_{'f64' if self.dtype == torch.float64 else 'f32'}")
@@ -293,6 +310,7 @@ class FusedSDDMM(_FusedBase):
         a.n_recv_a, a.a_src = n_recv_a, self.a_src.data_ptr()
         a.A_stage = self._A_full.data_ptr() + p.row.n_owned * self.row_bytes
         a.pull_order, a.n_waves, a.tiles_per_wave, a.wave_nnz = None, 0, 0, None
+        self._pull_config(a.pull)
         self.value_order = None   # None: results are stored in the plan's CSR order
         if overlap and (p.col.n_recv + n_recv_a) > 0 and p.nnz > 0:
             order, wave_nnz = self._plan_waves(p, n_recv_a)
@@ -344,7 +362,6 @@ class FusedSDDMM(_FusedBase):
         if Z > 1 and self.zreduce == "multimem":
             direct_push = 3   # nothing is pushed: the slice owners reduce through the multicast address
         a.direct_push = self.push_mode = direct_push
-        a.bulk_pull = int(self.bulk_pull)
 
     def _plan_waves(self, p, n_recv_a: int, target_waves: int | None = None):
         """Order of the pull tiles, their grouping into waves, and the order of the nonzeros by the wave that
@@ -357,7 +374,7 @@ class FusedSDDMM(_FusedBase):
         if target_waves is None:
             target_waves = int(os.environ.get("SP3_FUSED_WAVES", "4"))
         target_waves = max(1, min(MAX_WAVES, target_waves))
-        n_a, n_b = -(-n_recv_a // PULL_ROWS), -(-p.col.n_recv // PULL_ROWS)
+        n_a, n_b = -(-n_recv_a // self.tile_rows), -(-p.col.n_recv // self.tile_rows)
         n_pull = n_a + n_b
         key = np.concatenate([(np.arange(n_a) + 0.5) / max(n_a, 1), (np.arange(n_b) + 0.5) / max(n_b, 1)])
         code = np.concatenate([np.arange(n_a, dtype=np.int64) | (1 << 30), np.arange(n_b, dtype=np.int64)])
@@ -370,11 +387,11 @@ class FusedSDDMM(_FusedBase):
         wave_a, wave_b = ticket_of[:n_a] // tpw, ticket_of[n_a:] // tpw
         cls = np.zeros(p.nnz, np.int8)
         rem_b = p.colidx >= p.col.n_owned
-        cls[rem_b] = wave_b[(p.colidx[rem_b] - p.col.n_owned) // PULL_ROWS] + 1
+        cls[rem_b] = wave_b[(p.colidx[rem_b] - p.col.n_owned) // self.tile_rows] + 1
         if n_recv_a:
             rem_a = p.rowidx >= p.row.n_owned
             ca = np.zeros(p.nnz, np.int8)
-            ca[rem_a] = wave_a[(p.rowidx[rem_a] - p.row.n_owned) // PULL_ROWS] + 1
+            ca[rem_a] = wave_a[(p.rowidx[rem_a] - p.row.n_owned) // self.tile_rows] + 1
             np.maximum(cls, ca, out=cls)
         order = np.argsort(cls, kind="stable")
         wave_nnz = np.cumsum(np.bincount(cls, minlength=n_waves + 1)).astype(np.int64)
@@ -439,7 +456,8 @@ class FusedSpMM(_FusedBase):
         return self.region_sizes(plan, k_loc, self.reduce, dtype=self.dtype)
 
     def __init__(self, op, heap: SymmHeap | None = None, fabric=None, timeout_s: float = 30.0,
-                 reduce: str | None = None, red_v4: bool | None = None, bulk_pull: bool | None = None):
+                 reduce: str | None = None, red_v4: bool | None = None, bulk_pull: bool | None = None,
+                 overlap: bool = True):
         self.bulk_pull = _bulk_default(bulk_pull)
         if reduce is None:
             reduce = os.environ.get("SP3_FUSED_SPMM_REDUCE", "slots")
@@ -484,20 +502,43 @@ class FusedSpMM(_FusedBase):
         self.cptr = self._dev_i64(cptr)
         self.crows = self._dev_i32(crows if crows.size else [0])
         self.cslot = self._dev_i32(order if order.size else [0])
-        self.sched = cuda_ops.SpmmSchedule(op.rowptr)
+        a = self.args = _SpmmArgs()
+        self._pull_config(a.pull)
+        # Work items.  With rows to pull, the items are ordered by the pull wave that completes them and the
+        # nonzeros of long rows are sorted so that their owned columns come first: the kernel then works on
+        # what is there while the X rows arrive.  The re-ordered column indices and values are private copies
+        # (`_val_perm` maps them to the op's CSR arrays; `refresh_values` follows a change of the values).
+        self._val_perm, a.n_waves, a.tiles_per_wave, a.wave_items = None, 0, 0, None
+        if overlap and p.col.n_recv > 0 and p.nnz > 0:
+            target = max(1, min(MAX_WAVES, int(os.environ.get("SP3_FUSED_SPMM_WAVES", "4"))))
+            n_pull = -(-p.col.n_recv // self.tile_rows)
+            tpw = -(-n_pull // target)
+            n_waves = -(-n_pull // tpw)
+            cls = np.zeros(p.nnz, np.int8)
+            rem = p.colidx >= p.col.n_owned
+            cls[rem] = ((p.colidx[rem] - p.col.n_owned) // self.tile_rows) // tpw + 1
+            perm, items, first, npieces, class_items = cuda_ops.build_spmm_wave_items(p.rowptr, cls, n_waves + 1)
+            self.sched = cuda_ops.SpmmSchedule(op.rowptr, arrays=(items, first, npieces))
+            self._val_perm = torch.from_numpy(perm).to(self.device)
+            self._colidx = self._dev_i32(p.colidx[perm])
+            self._vals = op.vals[self._val_perm]
+            self._wave_items = self._dev_i32(class_items)
+            a.n_waves, a.tiles_per_wave, a.wave_items = int(n_waves), int(tpw), self._wave_items.data_ptr()
+        else:
+            self.sched = cuda_ops.SpmmSchedule(op.rowptr)
+            self._colidx, self._vals = op.colidx, op.vals
         carry, ldc = self.sched.carry_for(kp, self.dtype, self.device)
         self.slots = h.view("slots", self.dtype, (h.sizes["slots"] // self.es,))
         flag = np.zeros(max(1, rp.n_owned), np.uint8)
         flag[crows] = 1
         self.crow_flag = torch.from_numpy(flag).to(self.device)
-        a = self.args = _SpmmArgs()
         read_from = [col_r[q] for q in range(p.col.npeers) if p.col.recv_counts[q] > 0]
         readers = [col_r[q] for q in range(p.col.npeers) if p.col.send_counts[q] > 0]
         push_to = [row_r[q] for q in range(rp.npeers) if rp.recv_counts[q] > 0]
         contrib = [row_r[q] for q in range(rp.npeers) if rp.send_counts[q] > 0]
         self._fill_comm(a.comm, read_from, readers, push_to, contrib)
         a.nitems, a.items = self.sched.items.shape[0], self.sched.items.data_ptr()
-        a.rowptr, a.colidx, a.val = op.rowptr.data_ptr(), op.colidx.data_ptr(), op.vals.data_ptr()
+        a.rowptr, a.colidx, a.val = op.rowptr.data_ptr(), self._colidx.data_ptr(), self._vals.data_ptr()
         a.X_loc, a.ldx = self._X_full.data_ptr(), kp
         a.n_owned_x, a.n_recv_x = p.col.n_owned, p.col.n_recv
         a.x_src = self.x_src.data_ptr()
@@ -516,7 +557,12 @@ class FusedSpMM(_FusedBase):
         a.atomic, a.red_v4, a.crow_flag = int(self.atomic), int(bool(red_v4)), self.crow_flag.data_ptr()
         if self.atomic:
             a.parity_off_v = 0
-        a.bulk_pull = int(self.bulk_pull)
+
+    def refresh_values(self):
+        """Call after the values of the sparse matrix (`DistSpMM.vals`) were changed: the kernel reads a copy
+        of them in its own order when it overlaps pulls with compute."""
+        if self._val_perm is not None:
+            torch.index_select(self.op.vals, 0, self._val_perm, out=self._vals)
 
     def launch(self, Y: torch.Tensor, beta: float, phases=PH_ALL, new_epoch=True):
         if new_epoch:
