@@ -18,7 +18,9 @@ REF_SOURCES = ["comm_setup.cpp", "comm_stats.cpp", "core_ops.cpp", "dcomm_setup.
 
 
 def find_reference() -> Path | None:
-    for cand in (os.environ.get("SP3_REFERENCE_DIR"), "/root/reference", str(REF_DST / "SpComm3D")):
+    """The reference tree: the directory named by SP3_REFERENCE_DIR, else a checkout beside this repository
+    (../reference), else the copy already made under baseline/_ref."""
+    for cand in (os.environ.get("SP3_REFERENCE_DIR"), str(HERE.parent.parent / "reference"), str(REF_DST / "SpComm3D")):
         if cand and (Path(cand) / "src" / "core_ops.cpp").exists():
             return Path(cand)
     return None
@@ -31,7 +33,7 @@ def build(verbose=False) -> Path:
     if not (dst / "src" / "core_ops.cpp").exists():
         src = find_reference()
         if src is None:
-            raise RuntimeError("reference sources not found (expected /root/reference or baseline/_ref/SpComm3D)")
+            raise RuntimeError("reference sources not found (set SP3_REFERENCE_DIR, or place them under baseline/_ref/SpComm3D)")
         REF_DST.mkdir(exist_ok=True)
         shutil.copytree(src, dst, dirs_exist_ok=True)
     inputs = [HERE / "ref_driver.cpp", HERE / "mpi_shim" / "mpi_shim.cpp", HERE / "mpi_shim" / "mpi.h"]

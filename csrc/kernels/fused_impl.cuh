@@ -282,6 +282,69 @@ __device__ __forceinline__ bool bulk_pull_tile(BulkRing& br, const FusedComm& c,
     return ok;
 }
 
+// ---------------------------------------------------------------------------
+// Pulls and their waves, shared by both kernels.  The functions are deliberately not inlined: they run once per
+// pull ticket or per work ticket, and inlined into the kernels their state takes registers from the inner loops.
+// ---------------------------------------------------------------------------
+struct PullSide {
+    const float4* const* src;   // absolute address of every row of the receive list
+    float4* dst;                // where row 0 of the list lands; rows are `ld_v` vectors apart
+    int n_rows;
+};
+
+struct PullGate {
+    FusedComm c;                // a copy: pointing into the kernel's parameters would move all of them to local memory
+    PullSide side[2];           // SDDMM: [0] = B rows, [1] = staged A rows; SpMM: [0] = X rows
+    const int* order;           // ticket -> side << 30 | tile (null: all tiles of side 1, then side 0)
+    const long long* limit;     // shared memory: work runnable once the first w waves are complete, w = 0 .. n_waves
+    long long ld_v;
+    int nvec, tile_rows, n_pull, tiles1, tpw, n_waves;
+    bool bulk, pulls_left;
+    int waves_ready;            // leading waves this warp knows to be complete
+    BulkRing br;
+
+    // Serves one pull ticket; false when none is left (or a bulk copy timed out).
+    __device__ __noinline__ bool pull_one(int lane) {
+        const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
+        if (t >= n_pull) return false;
+        const int code = order ? __ldg(order + t) : (t < tiles1 ? (t | (1 << 30)) : t - tiles1);
+        const int tile = code & ((1 << 30) - 1);
+        const PullSide& sd = side[code >> 30];
+        const int r0 = tile * tile_rows;
+        const int r1 = r0 + tile_rows < sd.n_rows ? r0 + tile_rows : sd.n_rows;
+        if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, sd.src, sd.dst, nvec, lane)) return false; }
+        else pull_rows(r0, r1, sd.src, sd.dst, ld_v, nvec, lane);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+            atomicAdd(c.ctrl + C_WAVE0 + t / tpw, 1);
+            if (atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
+        }
+        return true;
+    }
+    __device__ __noinline__ void pull_all(int lane) {
+        while (pulls_left && !aborted(c)) pulls_left = pull_one(lane);
+    }
+    // Makes sure that every wave the work below `upto` needs is complete: a warp whose work is not ready serves a
+    // pull ticket (vector-load mode; every ticket is thus taken by a running warp and the wait cannot deadlock)
+    // and looks again; when no ticket is left for it, it waits, with a time limit, for the warps that still copy.
+    __device__ __noinline__ bool ensure_slow(long long upto, int lane) {
+        while (waves_ready < n_waves && upto > limit[waves_ready]) {
+            const int w = waves_ready;
+            const int want = (w + 1) * tpw <= n_pull ? tpw : n_pull - w * tpw;
+            if (ld_acquire_gpu(c.ctrl + C_WAVE0 + w) >= want) { ++waves_ready; continue; }
+            if (pulls_left) { pulls_left = pull_one(lane); continue; }
+            if (!wait_counter(c, C_WAVE0 + w, want, W_PULLS)) return false;
+            ++waves_ready;
+        }
+        return true;
+    }
+    __device__ __forceinline__ bool ensure(long long upto, int lane) {
+        if (waves_ready >= n_waves || upto <= limit[waves_ready]) return true;
+        return ensure_slow(upto, lane);
+    }
+};
+
 // Every warp calls this after its MAIN work; the last one to arrive publishes
 // DONE and PART for this rank.
 __device__ __forceinline__ void main_epilogue(const FusedComm& c, int lane, int nwarps) {
@@ -443,6 +506,7 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
     __shared__ unsigned long long a_bases[MAX_RANKS];
+    __shared__ long long wave_limit[MAX_WAVES + 1];
     extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: the pullers' rings, else nothing
     if (threadIdx.x < MAX_RANKS) a_bases[threadIdx.x] = threadIdx.x < a.world ? a.a_bases[threadIdx.x] : 0ull;
     const bool bulk = a.pull.pullers > 0;
@@ -469,67 +533,40 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         vec* Bv = reinterpret_cast<vec*>(a.B_loc);
         const long long ldb_v = a.ldb / VN;
         const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-        // pullers: in bulk mode the first warp of every block and nobody else; otherwise one warp in four,
+        // pullers: in bulk mode the first warps of every block and nobody else; otherwise one warp in four,
         // helped by any warp whose own units are not ready yet
         const bool is_puller = bulk ? (int)(threadIdx.x >> 5) < a.pull.pullers : (gwarp & 3) == 0;
-        bool pulls_left = n_pull > 0 && (!bulk || is_puller);
-        const long long n_free_units = a.nnz_free / per_unit;  // units that touch no pulled row
         const int n_waves = n_pull > 0 ? (a.n_waves > 0 ? a.n_waves : 1) : 0;
-        const int tpw = a.n_waves > 0 ? a.tiles_per_wave : (n_pull > 0 ? n_pull : 1);
-        auto pull_one = [&]() -> bool {
-            const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
-            if (t >= n_pull) return false;
-            const int code = a.pull_order ? __ldg(a.pull_order + t) : (t < n_pull_a ? (t | (1 << 30)) : t - n_pull_a);
-            const int tile = code & ((1 << 30) - 1);
-            const bool side_a = (code >> 30) != 0;
-            const int n_side = side_a ? a.n_recv_a : a.n_recv_b;
-            const float4* const* src = side_a ? a.a_src : a.b_src;
-            float4* dst = side_a ? reinterpret_cast<float4*>(a.A_stage)
-                                 : reinterpret_cast<float4*>(Bv + (long long)a.n_owned_b * ldb_v);
-            const int r0 = tile * PULL_ROWS;
-            const int r1 = r0 + PULL_ROWS < n_side ? r0 + PULL_ROWS : n_side;
-            if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, src, dst, a.nvec, lane)) return false; }
-            else pull_rows(r0, r1, src, dst, ldb_v, a.nvec, lane);
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) {
-                atomicAdd(c.ctrl + C_WAVE0 + t / tpw, 1);
-                if (atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
-            }
-            return true;
-        };
-        // Units runnable once the first w waves are complete (w = 0: the units that need no pulled row).
-        auto units_after = [&](int w) -> long long {
-            if (w >= n_waves) return n_units;
-            const long long z = a.wave_nnz ? a.wave_nnz[w] : a.nnz_free;
-            return z >= a.nnz ? n_units : z / per_unit;
-        };
-        int waves_ready = 0;   // leading waves this warp knows to be complete
-        // Makes sure that every wave units [.., u1) need is complete: a warp whose units are not ready serves a
-        // pull ticket (so every ticket is taken by a running warp and the wait cannot deadlock) and looks again;
-        // when no ticket is left it waits, with a time limit, for the warps that still copy.
-        auto ensure_waves = [&](long long u1) -> bool {
-            while (waves_ready < n_waves && u1 > units_after(waves_ready)) {
-                const int w = waves_ready;
-                const int want = (w + 1) * tpw <= n_pull ? tpw : n_pull - w * tpw;
-                if (ld_acquire_gpu(c.ctrl + C_WAVE0 + w) >= want) { ++waves_ready; continue; }
-                if (pulls_left) { pulls_left = pull_one(); continue; }
-                if (!wait_counter(c, C_WAVE0 + w, want, W_PULLS)) return false;
-                ++waves_ready;
-            }
-            return true;
-        };
+        // units runnable once the first w waves are complete (w = 0: the units that need no pulled row)
+        if ((int)threadIdx.x <= n_waves) {
+            const int w = threadIdx.x;
+            const long long z = w >= n_waves ? a.nnz : (a.wave_nnz ? a.wave_nnz[w] : a.nnz_free);
+            wave_limit[w] = z >= a.nnz ? n_units : z / per_unit;
+        }
+        __syncthreads();
+        PullGate gate;
+        gate.c = c;
+        gate.side[0] = {a.b_src, reinterpret_cast<float4*>(Bv + (long long)a.n_owned_b * ldb_v), a.n_recv_b};
+        gate.side[1] = {a.a_src, reinterpret_cast<float4*>(a.A_stage), a.n_recv_a};
+        gate.order = a.pull_order;
+        gate.limit = wave_limit;
+        gate.ld_v = ldb_v;
+        gate.nvec = a.nvec; gate.tile_rows = PULL_ROWS; gate.n_pull = n_pull; gate.tiles1 = n_pull_a;
+        gate.tpw = a.n_waves > 0 ? a.tiles_per_wave : (n_pull > 0 ? n_pull : 1);
+        gate.n_waves = n_waves;
+        gate.bulk = bulk;
+        gate.pulls_left = n_pull > 0 && (!bulk || is_puller);
+        gate.waves_ready = 0;
+        gate.br = br;
         // The pullers serve pull tickets until none are left while the others start on the units that need no
         // pulled row.
-        (void)n_free_units;
-        if (is_puller)
-            while (ok && pulls_left && !aborted(c)) pulls_left = pull_one();
+        if (is_puller && ok) gate.pull_all(lane);
         const int SDDMM_UNITS_PER_TICKET = per_ticket(n_units, nwarps, SDDMM_UNITS_PER_TICKET_MAX);
         while (ok) {
             const long long u0 = (long long)warp_ticket(c.ctrl + C_TICKET_WORK, lane, SDDMM_UNITS_PER_TICKET);
             if (u0 >= n_units) break;
             const long long u1 = u0 + SDDMM_UNITS_PER_TICKET < n_units ? u0 + SDDMM_UNITS_PER_TICKET : n_units;
-            ok = ensure_waves(u1);
+            ok = gate.ensure(u1, lane);
             if (!ok) break;
             for (long long u = u0; u < u1; ++u)
                 sddmm_warp_unit<real, G, R, U, RowsByPeerRef<real>, StorePartial, false>(
@@ -556,7 +593,7 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
                 }
             }
         }
-        while (ok && pulls_left) pulls_left = pull_one();  // no compute left but tiles remain (tiny blocks)
+        if (ok) gate.pull_all(lane);  // no compute left but tiles remain (tiny blocks)
         if (a.Z > 1 && !direct && !self_push && !in_switch) {
             // all partial values of this rank are in `part` once every warp has passed this point; then the
             // slices of the other fiber ranks travel as contiguous, fully coalesced remote stores
@@ -728,13 +765,20 @@ struct EmitOwnedOrAdd {
     }
 };
 
-template <int G, int R, int U, bool ATOMIC>
-__global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) {
+// Four resident blocks per SM (64 registers per thread) as long as a lane holds at most two vectors of a row:
+// left to itself the compiler takes 128 registers for the wave bookkeeping and halves the occupancy, which costs
+// the gather-bound inner loop far more than the few spills do.
+// GATED: the items follow the pull waves (wave_items given).  The other form pulls everything first and carries
+// no wave state: its inner loop keeps all 64 registers of a thread, which is worth 10-15 % on blocks that pull
+// nothing or little (meshes 1 x Y x Z).
+template <int G, int R, int U, bool ATOMIC, bool GATED>
+__global__ void __launch_bounds__(256, (R <= 2 ? 4 : 2)) fused_spmm_kernel(const FusedSpmmArgs a) {
     const FusedComm& c = a.comm;
     const int lane = threadIdx.x & 31;
     const int nwarps = (int)(((long long)gridDim.x * blockDim.x) >> 5);
     const int parity = c.epoch & 1;
     extern __shared__ __align__(128) unsigned char dyn_smem[];   // bulk mode: the pullers' rings, else nothing
+    __shared__ long long wave_limit[MAX_WAVES + 1];
     const bool bulk = a.pull.pullers > 0;
     const int PULL_ROWS = a.pull.tile_rows;
     BulkRing br = bulk_ring_init(dyn_smem, a.pull, threadIdx.x >> 5, lane);
@@ -780,68 +824,91 @@ __global__ void __launch_bounds__(256) fused_spmm_kernel(const FusedSpmmArgs a) 
         const long long ldx_v = a.ldx / VN;
         const EmitOwnedOrPush emit{reinterpret_cast<vec*>(a.Y), a.ldy / VN, (real)a.beta, a.n_owned_y, a.y_dst,
                                    parity ? a.parity_off_v : 0};
-        // Pullers: in bulk mode the first warps of every block; with vector loads one warp in four, helped by any
-        // warp whose own items are not ready yet.  The others start on the items that need no pulled row.
-        const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-        const bool is_puller = bulk ? (int)(threadIdx.x >> 5) < a.pull.pullers : (gwarp & 3) == 0;
-        bool pulls_left = n_pull > 0 && (!bulk || is_puller);
-        const int n_waves = n_pull > 0 ? (a.n_waves > 0 ? a.n_waves : 1) : 0;
-        const int tpw = a.n_waves > 0 ? a.tiles_per_wave : (n_pull > 0 ? n_pull : 1);
-        auto pull_one = [&]() -> bool {
-            const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
-            if (t >= n_pull) return false;
-            const int r0 = t * PULL_ROWS;
-            const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
-            float4* dst = reinterpret_cast<float4*>(Xv + (long long)a.n_owned_x * ldx_v);
-            if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, a.x_src, dst, a.nvec, lane)) return false; }
-            else pull_rows(r0, r1, a.x_src, dst, ldx_v, a.nvec, lane);
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) {
-                atomicAdd(c.ctrl + C_WAVE0 + t / tpw, 1);
-                if (atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
+        if constexpr (!GATED) {
+            // pull everything (bulk mode: the puller warps; else all warps), then compute
+            bool pulled = n_pull == 0;
+            float4* xdst = reinterpret_cast<float4*>(Xv + (long long)a.n_owned_x * ldx_v);
+            while (ok && (!bulk || (int)(threadIdx.x >> 5) < a.pull.pullers) && !aborted(c)) {
+                const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
+                if (t >= n_pull) break;
+                const int r0 = t * PULL_ROWS;
+                const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
+                if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, a.x_src, xdst, a.nvec, lane)) break; }
+                else pull_rows(r0, r1, a.x_src, xdst, ldx_v, a.nvec, lane);
+                __threadfence();
+                __syncwarp();
+                if (lane == 0 && atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
             }
-            return true;
-        };
-        // items runnable once the first w waves are complete (without wave data: none before the last pull)
-        auto items_after = [&](int w) -> int {
-            if (w >= n_waves) return a.nitems;
-            return a.wave_items ? __ldg(a.wave_items + w) : 0;
-        };
-        int waves_ready = 0;
-        auto ensure_waves = [&](int i1) -> bool {
-            while (waves_ready < n_waves && i1 > items_after(waves_ready)) {
-                const int w = waves_ready;
-                const int want = (w + 1) * tpw <= n_pull ? tpw : n_pull - w * tpw;
-                if (ld_acquire_gpu(c.ctrl + C_WAVE0 + w) >= want) { ++waves_ready; continue; }
-                if (pulls_left) { pulls_left = pull_one(); continue; }
-                if (!wait_counter(c, C_WAVE0 + w, want, W_PULLS)) return false;
-                ++waves_ready;
+            const int SPMM_ITEMS_PER_TICKET = per_ticket(a.nitems, nwarps, SPMM_ITEMS_PER_TICKET_MAX);
+            while (ok) {
+                const int i0 = warp_ticket(c.ctrl + C_TICKET_WORK, lane, SPMM_ITEMS_PER_TICKET);
+                if (i0 >= a.nitems) break;
+                if (!pulled) {
+                    ok = wait_counter(c, C_PULLS_DONE, n_pull, W_PULLS);
+                    pulled = true;
+                    if (!ok) break;
+                }
+                const int i1 = i0 + SPMM_ITEMS_PER_TICKET < a.nitems ? i0 + SPMM_ITEMS_PER_TICKET : a.nitems;
+                if constexpr (ATOMIC) {
+                    const EmitOwnedOrAdd add{reinterpret_cast<vec*>(a.Y), a.ldy / VN, (real)a.beta, a.n_owned_y, a.y_dst,
+                                             a.crow_flag, a.red_v4};
+                    for (int it = i0; it < i1; ++it)
+                        spmm_warp_item<real, G, R, U, EmitOwnedOrAdd, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
+                                                                              Xv, ldx_v, a.nvec, add, a.lg, lane);
+                } else {
+                    for (int it = i0; it < i1; ++it)
+                        spmm_warp_item<real, G, R, U, EmitOwnedOrPush, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
+                                                                               Xv, ldx_v, a.nvec, emit, a.lg, lane);
+                }
             }
-            return true;
-        };
-        if (is_puller)
-            while (ok && pulls_left && !aborted(c)) pulls_left = pull_one();
-        const int SPMM_ITEMS_PER_TICKET = per_ticket(a.nitems, nwarps, SPMM_ITEMS_PER_TICKET_MAX);
-        while (ok) {
-            const int i0 = warp_ticket(c.ctrl + C_TICKET_WORK, lane, SPMM_ITEMS_PER_TICKET);
-            if (i0 >= a.nitems) break;
-            const int i1 = i0 + SPMM_ITEMS_PER_TICKET < a.nitems ? i0 + SPMM_ITEMS_PER_TICKET : a.nitems;
-            ok = ensure_waves(i1);
-            if (!ok) break;
-            if constexpr (ATOMIC) {
-                const EmitOwnedOrAdd add{reinterpret_cast<vec*>(a.Y), a.ldy / VN, (real)a.beta, a.n_owned_y, a.y_dst,
-                                         a.crow_flag, a.red_v4};
-                for (int it = i0; it < i1; ++it)
-                    spmm_warp_item<real, G, R, U, EmitOwnedOrAdd, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
-                                                                          Xv, ldx_v, a.nvec, add, a.lg, lane);
-            } else {
-                for (int it = i0; it < i1; ++it)
-                    spmm_warp_item<real, G, R, U, EmitOwnedOrPush, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
-                                                                           Xv, ldx_v, a.nvec, emit, a.lg, lane);
+        } else {
+            // Pullers: in bulk mode the first warps of every block; with vector loads one warp in four, helped by any
+            // warp whose own items are not ready yet.  The others start on the items that need no pulled row.
+            const long long gwarp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+            const bool is_puller = bulk ? (int)(threadIdx.x >> 5) < a.pull.pullers : (gwarp & 3) == 0;
+            const int n_waves = n_pull > 0 ? (a.n_waves > 0 ? a.n_waves : 1) : 0;
+            // items runnable once the first w waves are complete (without wave data: none before the last pull)
+            if ((int)threadIdx.x <= n_waves) {
+                const int w = threadIdx.x;
+                wave_limit[w] = w >= n_waves ? a.nitems : (a.wave_items ? __ldg(a.wave_items + w) : 0);
             }
+            __syncthreads();
+            PullGate gate;
+            gate.c = c;
+            gate.side[0] = {a.x_src, reinterpret_cast<float4*>(Xv + (long long)a.n_owned_x * ldx_v), a.n_recv_x};
+            gate.side[1] = {nullptr, nullptr, 0};
+            gate.order = nullptr;
+            gate.limit = wave_limit;
+            gate.ld_v = ldx_v;
+            gate.nvec = a.nvec; gate.tile_rows = PULL_ROWS; gate.n_pull = n_pull; gate.tiles1 = 0;
+            gate.tpw = a.n_waves > 0 ? a.tiles_per_wave : (n_pull > 0 ? n_pull : 1);
+            gate.n_waves = n_waves;
+            gate.bulk = bulk;
+            gate.pulls_left = n_pull > 0 && (!bulk || is_puller);
+            gate.waves_ready = 0;
+            gate.br = br;
+            if (is_puller && ok) gate.pull_all(lane);
+            const int SPMM_ITEMS_PER_TICKET = per_ticket(a.nitems, nwarps, SPMM_ITEMS_PER_TICKET_MAX);
+            while (ok) {
+                const int i0 = warp_ticket(c.ctrl + C_TICKET_WORK, lane, SPMM_ITEMS_PER_TICKET);
+                if (i0 >= a.nitems) break;
+                const int i1 = i0 + SPMM_ITEMS_PER_TICKET < a.nitems ? i0 + SPMM_ITEMS_PER_TICKET : a.nitems;
+                ok = gate.ensure(i1, lane);
+                if (!ok) break;
+                if constexpr (ATOMIC) {
+                    const EmitOwnedOrAdd add{reinterpret_cast<vec*>(a.Y), a.ldy / VN, (real)a.beta, a.n_owned_y, a.y_dst,
+                                             a.crow_flag, a.red_v4};
+                    for (int it = i0; it < i1; ++it)
+                        spmm_warp_item<real, G, R, U, EmitOwnedOrAdd, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
+                                                                              Xv, ldx_v, a.nvec, add, a.lg, lane);
+                } else {
+                    for (int it = i0; it < i1; ++it)
+                        spmm_warp_item<real, G, R, U, EmitOwnedOrPush, false>(__ldg(a.items + it), a.rowptr, a.colidx, a.val,
+                                                                               Xv, ldx_v, a.nvec, emit, a.lg, lane);
+                }
+            }
+            if (ok) gate.pull_all(lane);  // no item left but tiles remain (tiny blocks)
         }
-        while (ok && pulls_left) pulls_left = pull_one();  // no item left but tiles remain (tiny blocks)
         main_epilogue(c, lane, nwarps);
     }
     if (c.phases & PH_FINISH) {
@@ -960,9 +1027,12 @@ SP3_API int SP3_FUSED_CAT(sp3_fused_spmm_, SP3_FUSED_SUFFIX)(const void* args, v
     if (e != cudaSuccess) return (int)e;
     int G, R, rc = 0;
     pick_shape(a.nvec, &G, &R, true);
+    const bool gated = a.wave_items != nullptr && a.n_waves > 0 && a.n_recv_x > 0;
 #define SP3_FSPMM(GG, RR)                                                                        \
-    rc = a.atomic ? launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true>, a, st)   \
-                  : launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false>, a, st)
+    rc = a.atomic ? (gated ? launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true, true>, a, st)     \
+                           : launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), true, false>, a, st))   \
+                  : (gated ? launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false, true>, a, st)    \
+                           : launch_resident(fused_spmm_kernel<GG, RR, (RR >= 8 ? 2 : 4), false, false>, a, st))
     SP3_DISPATCH_GR(SP3_FSPMM)
 #undef SP3_FSPMM
     return rc ? rc : (int)cudaGetLastError();

@@ -509,6 +509,8 @@ class FusedSpMM(_FusedBase):
         # what is there while the X rows arrive.  The re-ordered column indices and values are private copies
         # (`_val_perm` maps them to the op's CSR arrays; `refresh_values` follows a change of the values).
         self._val_perm, a.n_waves, a.tiles_per_wave, a.wave_items = None, 0, 0, None
+        if os.environ.get("SP3_FUSED_SPMM_WAVES") == "0":   # tuning: no overlap, compute after the last pull
+            overlap = False
         if overlap and p.col.n_recv > 0 and p.nnz > 0:
             target = max(1, min(MAX_WAVES, int(os.environ.get("SP3_FUSED_SPMM_WAVES", "4"))))
             n_pull = -(-p.col.n_recv // self.tile_rows)

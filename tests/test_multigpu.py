@@ -56,6 +56,28 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
             if yref.numel():
                 err = (y.cpu().double() - yref).abs().max()
                 assert err <= 2e-5 * max(1.0, yref.abs().max()) * 8, (variant, "spmm", float(err))
+    # the reference's value type on the fused kernels (fp64), with an inner dimension that Z does not divide evenly
+    k64 = k - 3
+    sd = DistSDDMM(plan, groups, k64, torch.float64, dev, "fused", fabric=fabric, timeout_s=10.0)
+    sp = DistSpMM(plan, groups, k64, torch.float64, dev, "fused", fabric=fabric, timeout_s=10.0)
+    A = generate.fill_rows(np.arange(m.nrows), k64, 0, k64, seed=9, stream=1, dtype=np.float64)
+    B = generate.fill_rows(np.arange(m.ncols), k64, 0, k64, seed=9, stream=2, dtype=np.float64)
+    sd.fill_owned(sd.A_owned, plan.row.owned_gids, seed=9, stream=1)
+    sd.fill_owned(sd.B_owned, plan.col.owned_gids, seed=9, stream=2)
+    sp.fill_owned(sp.X_owned, plan.col.owned_gids, seed=9, stream=2)
+    sd.poison_unowned()
+    sp.poison_unowned()
+    c, y = sd.run(), sp.run()
+    pos = sd.owned_positions()
+    mine = CooMatrix(m.nrows, m.ncols, plan.global_rows()[pos], plan.global_cols()[pos], plan.vals[pos])
+    ref = oracle.sddmm_ref(mine, A, B)
+    if ref.numel():
+        assert (c.cpu() - ref).abs().max() <= 1e-11 * max(1.0, ref.abs().max()) * k64, "fp64 fused sddmm"
+    ko, kw_ = split_k(k64, mesh.Z, plan.coords[2])
+    yref = oracle.spmm_ref(m, B)[plan.row.owned_gids][:, ko:ko + kw_]
+    if yref.numel():
+        assert (y.cpu() - yref).abs().max() <= 1e-11 * max(1.0, yref.abs().max()) * 64, "fp64 fused spmm"
+    del sd, sp
     # Z reduction inside the NVSwitch (multimem.ld_reduce over a multicast-bound buffer of the fiber).  No rank
     # raises while the buffer is bound: errors are collected, agreed on, and reported after the release.
     # Exercised where the fiber is the whole job (1x1xZ): multicast objects over sub-groups are not verified yet.
