@@ -233,9 +233,24 @@ __device__ __forceinline__ BulkRing bulk_ring_init(unsigned char* dyn_smem, cons
 // no padding between rows).  All lanes of one warp call it.  Returns false when a load did not arrive in time
 // (status recorded, abort raised); the copies still in flight are then given the same time again before the
 // warp moves on, because their destination is this block's shared memory.
+//
+// drain = true: returns when the stores of this tile are complete.  drain = false: returns as soon as the last
+// store is issued, so that the next tile's loads start without a pipeline bubble; `after_first_store` is called
+// once the first store group of this tile is committed and all older groups (the previous tile's stores) are
+// complete -- the place to publish the previous tile.  The caller publishes the last tile after bulk_drain().
+// Until all bulk stores of this warp are complete and ordered before the ordinary accesses that publish them.
+__device__ __forceinline__ void bulk_drain(int lane) {
+    if (lane == 0) {
+        bulk_wait<0>();
+        fence_async_proxy();
+    }
+    __syncwarp();
+}
+
+template <typename F>
 __device__ __forceinline__ bool bulk_pull_tile(BulkRing& br, const FusedComm& c, int r0, int r1,
                                                const float4* const* __restrict__ src, float4* __restrict__ dst,
-                                               int nvec, int lane) {
+                                               int nvec, int lane, bool drain, F&& after_first_store) {
     const unsigned row_bytes = (unsigned)nvec * 16u;
     int rps = (int)(br.stage_bytes / row_bytes);   // rows per stage
     rps = rps < 1 ? 1 : rps;
@@ -270,15 +285,19 @@ __device__ __forceinline__ bool bulk_pull_tile(BulkRing& br, const FusedComm& c,
                     bulk_store(dst + (long long)(r0 + c0) * nvec, br.ring + st * br.stage_bytes, (unsigned)cn * row_bytes);
                     bulk_commit();
                 }
+                if (pc == 0 && !drain) {
+                    if (lane == 0) {
+                        bulk_wait<1>();        // every group but the one just committed: the previous tile is complete
+                        fence_async_proxy();
+                    }
+                    __syncwarp();
+                    after_first_store();
+                }
             }
         }
     }
     br.g += nch;
-    if (lane == 0) {
-        bulk_wait<0>();        // the stores of this tile are complete ...
-        fence_async_proxy();   // ... and ordered before the ordinary accesses that publish the tile
-    }
-    __syncwarp();
+    if (drain) bulk_drain(lane);
     return ok;
 }
 
@@ -301,29 +320,51 @@ struct PullGate {
     int nvec, tile_rows, n_pull, tiles1, tpw, n_waves;
     bool bulk, pulls_left;
     int waves_ready;            // leading waves this warp knows to be complete
+    int pending;                // bulk mode: ticket whose stores are issued but not yet published (-1: none)
     BulkRing br;
 
-    // Serves one pull ticket; false when none is left (or a bulk copy timed out).
-    __device__ __noinline__ bool pull_one(int lane) {
-        const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
-        if (t >= n_pull) return false;
-        const int code = order ? __ldg(order + t) : (t < tiles1 ? (t | (1 << 30)) : t - tiles1);
-        const int tile = code & ((1 << 30) - 1);
-        const PullSide& sd = side[code >> 30];
-        const int r0 = tile * tile_rows;
-        const int r1 = r0 + tile_rows < sd.n_rows ? r0 + tile_rows : sd.n_rows;
-        if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, sd.src, sd.dst, nvec, lane)) return false; }
-        else pull_rows(r0, r1, sd.src, sd.dst, ld_v, nvec, lane);
+    // Tells the other warps that the rows of ticket t are in the local block.
+    __device__ __forceinline__ void publish(int t, int lane) {
         __threadfence();
         __syncwarp();
         if (lane == 0) {
             atomicAdd(c.ctrl + C_WAVE0 + t / tpw, 1);
             if (atomicAdd(c.ctrl + C_PULLS_DONE, 1) == n_pull - 1) stamp(c, T_PULLED);
         }
+    }
+    // Publishes the tile that is still in flight (bulk mode); before this warp waits for anybody or leaves.
+    __device__ __forceinline__ void flush(int lane) {
+        if (pending >= 0) {
+            bulk_drain(lane);
+            publish(pending, lane);
+            pending = -1;
+        }
+    }
+    // Serves one pull ticket; false when none is left (or a bulk copy timed out).  In bulk mode the tile is
+    // published when the next one is under way (or by flush), so that the copies of consecutive tiles overlap.
+    __device__ __noinline__ bool pull_one(int lane) {
+        const int t = warp_ticket(c.ctrl + C_TICKET_MAIN, lane);
+        if (t >= n_pull) { flush(lane); return false; }
+        const int code = order ? __ldg(order + t) : (t < tiles1 ? (t | (1 << 30)) : t - tiles1);
+        const int tile = code & ((1 << 30) - 1);
+        const PullSide& sd = side[code >> 30];
+        const int r0 = tile * tile_rows;
+        const int r1 = r0 + tile_rows < sd.n_rows ? r0 + tile_rows : sd.n_rows;
+        if (bulk) {
+            const bool ok = bulk_pull_tile(br, c, r0, r1, sd.src, sd.dst, nvec, lane, false, [&]() {
+                if (pending >= 0) { publish(pending, lane); pending = -1; }
+            });
+            if (!ok) { bulk_drain(lane); pending = -1; return false; }
+            pending = t;
+            return true;
+        }
+        pull_rows(r0, r1, sd.src, sd.dst, ld_v, nvec, lane);
+        publish(t, lane);
         return true;
     }
     __device__ __noinline__ void pull_all(int lane) {
         while (pulls_left && !aborted(c)) pulls_left = pull_one(lane);
+        flush(lane);
     }
     // Makes sure that every wave the work below `upto` needs is complete: a warp whose work is not ready serves a
     // pull ticket (vector-load mode; every ticket is thus taken by a running warp and the wait cannot deadlock)
@@ -334,6 +375,7 @@ struct PullGate {
             const int want = (w + 1) * tpw <= n_pull ? tpw : n_pull - w * tpw;
             if (ld_acquire_gpu(c.ctrl + C_WAVE0 + w) >= want) { ++waves_ready; continue; }
             if (pulls_left) { pulls_left = pull_one(lane); continue; }
+            flush(lane);   // never wait while a tile of this warp is unpublished
             if (!wait_counter(c, C_WAVE0 + w, want, W_PULLS)) return false;
             ++waves_ready;
         }
@@ -557,6 +599,7 @@ __global__ void __launch_bounds__(256, sddmm_min_blocks(R)) fused_sddmm_kernel(c
         gate.bulk = bulk;
         gate.pulls_left = n_pull > 0 && (!bulk || is_puller);
         gate.waves_ready = 0;
+        gate.pending = -1;
         gate.br = br;
         // The pullers serve pull tickets until none are left while the others start on the units that need no
         // pulled row.
@@ -833,7 +876,7 @@ __global__ void __launch_bounds__(256, (R <= 2 ? 4 : 2)) fused_spmm_kernel(const
                 if (t >= n_pull) break;
                 const int r0 = t * PULL_ROWS;
                 const int r1 = r0 + PULL_ROWS < a.n_recv_x ? r0 + PULL_ROWS : a.n_recv_x;
-                if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, a.x_src, xdst, a.nvec, lane)) break; }
+                if (bulk) { if (!bulk_pull_tile(br, c, r0, r1, a.x_src, xdst, a.nvec, lane, true, [] {})) break; }
                 else pull_rows(r0, r1, a.x_src, xdst, ldx_v, a.nvec, lane);
                 __threadfence();
                 __syncwarp();
@@ -886,6 +929,7 @@ __global__ void __launch_bounds__(256, (R <= 2 ? 4 : 2)) fused_spmm_kernel(const
             gate.bulk = bulk;
             gate.pulls_left = n_pull > 0 && (!bulk || is_puller);
             gate.waves_ready = 0;
+        gate.pending = -1;
             gate.br = br;
             if (is_puller && ok) gate.pull_all(lane);
             const int SPMM_ITEMS_PER_TICKET = per_ticket(a.nitems, nwarps, SPMM_ITEMS_PER_TICKET_MAX);

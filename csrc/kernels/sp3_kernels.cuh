@@ -1,6 +1,6 @@
 // Warp-level bodies of the SDDMM and SpMM kernels, shared by the local
 // kernels (local_ops.cu) and the fused compute+communication kernels
-// (fused_ops.cu).  Where dense rows come from and where results go is a
+// (fused_impl.cuh).  Where dense rows come from and where results go is a
 // template policy, so both families run the same inner loops:
 //
 //   SDDMM   A rows:  RowsByStride (one local block) | RowsByPeerRef (rows that

@@ -1,4 +1,4 @@
-"""Front end of the fused compute+communication kernels (csrc/kernels/fused_ops.cu).
+"""Front end of the fused compute+communication kernels (csrc/kernels/fused_impl.cuh).
 
 `FusedSDDMM` / `FusedSpMM` own the symmetric heap of one distributed op, turn
 its plan into the pointer tables the kernel needs (absolute addresses of dense

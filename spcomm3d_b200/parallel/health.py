@@ -12,7 +12,7 @@ The reference has none: a missing communicator ends in `exit(EXIT_FAILURE)`
 * collectives of the library path end with an error after the process
   group's timeout when a peer never joins, and the device-side waits of the
   fused kernels are bounded and report through a status word
-  (csrc/kernels/fused_ops.cu).
+  (csrc/kernels/fused_impl.cuh).
 
 There is no elastic resize: a failed rank ends the job cleanly.
 """

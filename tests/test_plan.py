@@ -153,3 +153,48 @@ def test_degenerate_matrices(meshstr):
             if p.coords[2] == 0:
                 total += float(c.sum())
         assert total == pytest.approx(8 * float(m.vals.sum()))
+
+
+def test_spmm_wave_items_cover_every_nonzero_once_in_class_order():
+    """Work items of the wave-gated SpMM: the re-ordering stays inside rows, long rows are cut into pieces of
+    one class each, every nonzero belongs to exactly one item, items come in non-decreasing class order and the
+    per-class counts are their prefix sums."""
+    from spcomm3d_b200.ops.cuda_ops import PIECE_SHIFT, build_spmm_items, build_spmm_wave_items
+    rng = np.random.default_rng(0)
+    nrows = 3000
+    deg = rng.poisson(4, nrows)
+    deg[rng.choice(nrows, 6, replace=False)] = [700, 1300, 513, 2500, 600, 900]
+    rowptr = np.zeros(nrows + 1, np.int64)
+    rowptr[1:] = np.cumsum(deg)
+    nnz = int(rowptr[-1])
+    cls = rng.integers(0, 4, nnz).astype(np.int8)
+    perm, items, first, npieces, class_items = build_spmm_wave_items(rowptr, cls, 4, long_row=512)
+    assert sorted(perm.tolist()) == list(range(nnz))
+    rows_of = np.repeat(np.arange(nrows), deg)
+    assert np.array_equal(rows_of[perm], rows_of)           # nonzeros stay in their rows
+    cp = cls[perm]
+    cover = np.zeros(nnz, np.int64)
+    last, seen_pieces, per_class = -1, set(), np.zeros(4, np.int64)
+    for it in items:
+        if it[3] < 0:
+            b, e = rowptr[it[0]], rowptr[it[1]]
+            c = int(cp[b:e].max()) if e > b else 0
+        else:
+            b, e = int(it[1]), int(it[2])
+            c = int(cp[b:e].max())
+            assert cp[b:e].min() == c and 0 < e - b <= 512 and rowptr[it[0]] <= b < e <= rowptr[it[0] + 1]
+            lr, pn = it[3] & ((1 << PIECE_SHIFT) - 1), it[3] >> PIECE_SHIFT
+            assert pn < npieces[lr] and (lr, pn) not in seen_pieces
+            seen_pieces.add((lr, pn))
+        cover[b:e] += 1
+        assert c >= last
+        last = c
+        per_class[c] += 1
+    assert (cover == 1).all()
+    assert np.array_equal(np.cumsum(per_class), class_items)
+    assert len(seen_pieces) == int(npieces.sum()) and np.array_equal(first, np.cumsum(npieces) - npieces)
+    # the plain schedule numbers its pieces the same way
+    it2, f2, n2 = build_spmm_items(rowptr, long_row=512)
+    pieces = it2[it2[:, 3] >= 0]
+    got = sorted((int(w) & ((1 << PIECE_SHIFT) - 1), int(w) >> PIECE_SHIFT) for w in pieces[:, 3])
+    assert got == sorted((lr, j) for lr in range(len(n2)) for j in range(int(n2[lr])))
