@@ -21,6 +21,7 @@ from .common import Runtime, base_parser, klist
 def run_instances(rt, plan, args, kernel_cls, default_variants, fill):
     for k in klist(args.klist):
         for variant in rt.variants(args, default_variants):
+            rt.checkpoint()
             try:
                 op = kernel_cls(plan, rt.groups, k, rt.dtype, rt.device, variant)
             except ValueError as e:

@@ -41,6 +41,9 @@ def base_parser(prog: str, description: str) -> argparse.ArgumentParser:
                     help="write every rank's plan to PREFIX.rank<r>.npz after building it")
     ap.add_argument("--load-plan", default=None, metavar="PREFIX",
                     help="read the plans written by --save-plan instead of partitioning the matrix again")
+    ap.add_argument("--heartbeat", action="store_true",
+                    help="ranks publish their progress in the process-group store; before every instance each rank "
+                         "checks that all others have arrived and stops with a message naming the missing ones")
     ap.add_argument("-v", dest="verbose", action="store_true")
     return ap
 
@@ -78,6 +81,19 @@ class Runtime:
         self.groups = MeshGroups.create(self.mesh) if self.world > 1 else None
         self.dtype = {"fp32": torch.float32, "fp64": torch.float64, None:
                       (torch.float32 if want_cuda else torch.float64)}[args.dtype]
+        self.heartbeat, self._beats = None, 0
+        if getattr(args, "heartbeat", False) and self.world > 1:
+            from ..parallel.health import Heartbeat
+            self.heartbeat = Heartbeat(self.rank, self.world)
+
+    def checkpoint(self, wait_s: float = 60.0):
+        """With --heartbeat: publishes that this rank reached the next checkpoint and raises `RankFailure`
+        naming the ranks that do not arrive within `wait_s` (a rank only ever leaves between steps, so the
+        others learn of it here, on the host, before their next launch)."""
+        if self.heartbeat is not None:
+            self._beats += 1
+            self.heartbeat.beat(self._beats)
+            self.heartbeat.require_alive(self._beats, wait_s=wait_s)
 
     def variants(self, args, default):
         v = args.variant.split(",") if args.variant else list(default)

@@ -57,7 +57,9 @@ def test_bench_cli_under_torchrun_prints_parsable_lines(tmp_path):
     assert pre["P"] == 4 and pre["avg"][1] == pre["avg"][3]  # everything sent is received
     dense = [stats.parse_line(l) for l in lines if "dense sddmm PRE" in l and " 16 2 " in l][0]
     assert dense["avg"][3] >= pre["avg"][3]
-    out = _torchrun(2, "spcomm3d_b200.cli.bench_spmm", "-k", "8", "-c", "1", "-i", "1", "--device", "cpu", path)
+    # --heartbeat: every rank publishes its progress and checks the others before each instance
+    out = _torchrun(2, "spcomm3d_b200.cli.bench_spmm", "-k", "8", "-c", "1", "-i", "1", "--device", "cpu", "--heartbeat",
+                    path)
     assert out.returncode == 0, out.stderr[-2000:]
     assert sum(l.startswith("web ") for l in out.stdout.splitlines()) == 3 * 2
 
