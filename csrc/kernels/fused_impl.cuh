@@ -7,17 +7,23 @@
 // src/distributed_comp.cpp:17-76 for SpMM and :141-284 for SDDMM, with the
 // staging copies of src/comm.hpp:90-103,166-189), every rank's kernel
 //
-//   * pulls the dense rows it needs on the column side (B for SDDMM, X for
-//     SpMM) straight out of the owners' memory over NVLink into its local
-//     block, tile by tile, while other warps already compute;
-//   * reads the row-side operand of SDDMM (A rows) directly from the owner's
-//     memory -- each such row is consumed by one work unit, so it crosses
-//     NVLink exactly once and is never staged;
-//   * SDDMM: keeps its partial dot products in a local array and, as soon as
-//     all of them exist, stores the slice of every other fiber rank into that
-//     rank's value buffer with contiguous, coalesced remote stores; each rank
-//     then sums the Z partial vectors of its own slice (the reduce-scatter of
-//     src/denseComm.hpp:35-40 becomes remote stores + a local sum);
+//   * pulls the dense rows it needs (B and, staged, A rows for SDDMM; X rows
+//     for SpMM) straight out of the owners' memory over NVLink into its local
+//     block: the first warp of every block issues one `cp.async.bulk` copy per
+//     row into a shared-memory ring and one bulk store per filled stage, so no
+//     compute warp ever waits for a remote load (a form with vector loads by
+//     the pulling warps is kept as an option, as is reading remote A rows in
+//     place through peer references);
+//   * computes wave by wave: the pull tickets are grouped into a few waves
+//     with one completion counter each, the work (nonzeros for SDDMM, items
+//     and pieces of hub rows for SpMM) is sorted by the wave that completes
+//     it, and a work ticket waits only for the waves it needs;
+//   * SDDMM: keeps its partial dot products in a local array in compute order
+//     and sends the ranges that belong to other fiber ranks as contiguous
+//     remote stores right after each ticket; each rank then sums the Z partial
+//     vectors of its own slice (the reduce-scatter of src/denseComm.hpp:35-40
+//     becomes remote stores + a local sum, or one `multimem.ld_reduce` per 16
+//     bytes where the fiber is bound to a multicast object);
 //   * SpMM: stores finished partial rows of rows it does not own directly into
 //     a slot in the owner's memory; the owner adds its own partial and the
 //     slots in ascending source order (bitwise reproducible), which is the
