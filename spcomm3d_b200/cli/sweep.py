@@ -108,7 +108,8 @@ def main(argv=None):
                     ms_max = float(mx[0])
                     roof = stats.roofline(op.flops() / mesh.size, float(mx[1]), gather_bytes, ms_max,
                                           nvlink_gbs=NVLINK_GBS, hbm_gbs=HBM_GBS)
-                    rec = {"kernel": cls.kernel, "mesh": str(mesh), "variant": variant, "k": k, "matrix": plan.name,
+                    rec = {"kernel": cls.kernel, "mesh": str(mesh), "variant": variant, "path": op.variant, "k": k,
+                           "matrix": plan.name,
                            "ms": round(ms_max, 4), "gflops": round(op.flops() / ms_max / 1e6, 1),
                            "comm_bytes_max_rank": float(mx[1]), "comm_bytes_total": float(sm[2]),
                            "roofline": {kk: (round(v, 4) if isinstance(v, float) else v) for kk, v in roof.items()}}

@@ -33,6 +33,10 @@ def _rank_main(rank, world, meshstr, gen, k, variants):
         kw = {"fabric": fabric, "timeout_s": 10.0, "reduce": reduce} if variant == "fused" else {}
         sd = DistSDDMM(plan, groups, k, torch.float32, dev, variant, **kw)
         sp = DistSpMM(plan, groups, k, torch.float32, dev, variant, **kw)
+        if variant == "fused" and mesh.X == mesh.Y == 1:
+            # nothing to pull on a 1 x 1 x Z mesh: "fused" runs the local kernels + the library reduce-scatter
+            assert sd.variant == sp.variant == "sparseNRB" and not hasattr(sd, "_fused")
+            assert sd.alg_name("PRE").startswith("sparseNB")
         for epoch in range(2):
             A = generate.fill_rows(np.arange(m.nrows), k, 0, k, seed=5 + epoch, stream=1, dtype=np.float64)
             B = generate.fill_rows(np.arange(m.ncols), k, 0, k, seed=5 + epoch, stream=2, dtype=np.float64)
