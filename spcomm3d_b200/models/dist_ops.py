@@ -44,7 +44,7 @@ import numpy as np
 import torch
 
 from ..ops import local
-from ..parallel.comm import DenseExchange, FiberReduce, PhaseTimer, SparseExchange
+from ..parallel.comm import CombinedExpand, DenseExchange, FiberReduce, PhaseTimer, SparseExchange
 from ..parallel.mesh import MeshGroups, split_k
 from ..parallel.plan import RankPlan
 from ..utils import generate
@@ -202,9 +202,16 @@ class DistSDDMM(_Dist3DOp):
             self.A_loc, self.B_loc = self._alloc_local(p.row), self._alloc_local(p.col)
         self.A_owned, self.B_owned = self.A_loc[:p.row.n_owned], self.B_loc[:p.col.n_owned]
         self.partial = torch.zeros(p.nnz, dtype=dtype, device=self.device)
+        self.exAB = None
         if variant in ("sparse", "sparseNRB"):
             self.exA = self._exchange(p.row, self._row_group)
             self.exB = self._exchange(p.col, self._col_group)
+            # "sparse": A and B rows in one exchange over the plane, as the reference's combined handle does
+            # (src/comm_setup.cpp:434-577); the batched point-to-point transport keeps the two line exchanges
+            if (variant == "sparse" and groups is not None and self.mesh.xy_size > 1
+                    and os.environ.get("SP3_TRANSPORT", "alltoall") == "alltoall"):
+                self.exAB = CombinedExpand(p.row, p.col, groups.plane, self.mesh, p.coords, self.k_loc, dtype,
+                                           self.device, self.timer)
         if variant != "fused":
             self.fiber = FiberReduce(p.nnz, self.mesh.Z, p.coords[2], self._fiber_group, dtype, self.device)
         # opt-in: dense (128-row x 64-column) panels on the tensor cores (TF32), the rest on the gather kernel
@@ -234,8 +241,11 @@ class DistSDDMM(_Dist3DOp):
                 c = self.fiber(self.partial)
         else:
             with t.span("comm1"):
-                self.exA.expand(self.A_loc)
-                self.exB.expand(self.B_loc)
+                if self.exAB is not None:
+                    self.exAB.expand(self.A_loc, self.B_loc)
+                else:
+                    self.exA.expand(self.A_loc)
+                    self.exB.expand(self.B_loc)
             with t.span("comp"):
                 if self._panels is not None:
                     self._panels.run(self.A_loc, self.B_loc, self.partial)

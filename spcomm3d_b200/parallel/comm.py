@@ -181,6 +181,64 @@ class SparseExchange:
         return buf
 
 
+class CombinedExpand:
+    """Both operands of an SDDMM in one exchange: the A rows a rank's row-line peers need and the B rows its
+    column-line peers need travel in a single all_to_all over the xy plane, through one send and one receive
+    staging buffer -- the reference's "sparse" instance (one SparseComm handle for A and B rows,
+    src/comm_setup.cpp:434-577, run at src/distributed_comp.cpp:157-165).
+
+    Plane ranks ascend as x * Y + y, so the peers of rank (x, y) come in the order: column-line peers with a
+    smaller x, the whole row line, column-line peers with a larger x.  Both staging buffers are laid out that
+    way, which makes packing and unpacking three contiguous pieces each."""
+
+    def __init__(self, row: SidePlan, col: SidePlan, plane_group, mesh, coords, k_loc: int, dtype, device, timer=None):
+        self.row, self.col, self.group, self.k, self.timer = row, col, plane_group, k_loc, timer
+        self.device = torch.device(device)
+        X, Y = mesh.X, mesh.Y
+        x, y = coords[0], coords[1]
+        send = np.zeros(X * Y, np.int64)
+        recv = np.zeros(X * Y, np.int64)
+        for j in range(Y):
+            send[x * Y + j] += row.send_counts[j]
+            recv[x * Y + j] += row.recv_counts[j]
+        for i in range(X):
+            send[i * Y + y] += col.send_counts[i]
+            recv[i * Y + y] += col.recv_counts[i]
+        self.send_split, self.recv_split = _splits(send), _splits(recv)
+        so, ro = col.send_offsets(), col.recv_offsets()
+        self.b_send_lo, self.b_recv_lo = int(so[x]), int(ro[x])   # rows for / from column peers with a smaller x
+        self.send_idx_a = torch.from_numpy(row.send_idx).to(self.device)
+        self.send_idx_b = torch.from_numpy(col.send_idx).to(self.device)
+        self.send_buf = torch.empty(row.n_send + col.n_send, k_loc, dtype=dtype, device=self.device)
+        self.recv_buf = torch.empty(row.n_recv + col.n_recv, k_loc, dtype=dtype, device=self.device)
+
+    def _span(self, name):
+        return self.timer.span(name) if self.timer is not None else _NullSpan()
+
+    def stats(self):
+        r, c = self.row, self.col
+        return ((r.out_degree() + c.out_degree(), (r.n_send + c.n_send) * self.k),
+                (r.in_degree() + c.in_degree(), (r.n_recv + c.n_recv) * self.k))
+
+    def expand(self, A: torch.Tensor, B: torch.Tensor):
+        """A[:n_owned], B[:n_owned] hold the owned rows; fills A[n_owned:] and B[n_owned:]."""
+        r, c = self.row, self.col
+        lo_s, lo_r = self.b_send_lo, self.b_recv_lo
+        with self._span("commcpy"):
+            if lo_s:
+                local.gather_rows(self.send_idx_b[:lo_s], B[:c.n_owned], self.send_buf[:lo_s])
+            if r.n_send:
+                local.gather_rows(self.send_idx_a, A[:r.n_owned], self.send_buf[lo_s:lo_s + r.n_send])
+            if c.n_send > lo_s:
+                local.gather_rows(self.send_idx_b[lo_s:], B[:c.n_owned], self.send_buf[lo_s + r.n_send:])
+        dist.all_to_all_single(self.recv_buf, self.send_buf, self.recv_split, self.send_split, group=self.group)
+        with self._span("commcpy"):
+            B[c.n_owned:c.n_owned + lo_r].copy_(self.recv_buf[:lo_r])
+            A[r.n_owned:].copy_(self.recv_buf[lo_r:lo_r + r.n_recv])
+            B[c.n_owned + lo_r:].copy_(self.recv_buf[lo_r + r.n_recv:])
+        return A, B
+
+
 class _NullSpan:
     def __enter__(self):
         return self
