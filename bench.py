@@ -165,7 +165,7 @@ def run_ours(args):
     from spcomm3d_b200.parallel import health
     from spcomm3d_b200.parallel.mesh import Mesh3D, MeshGroups
     from spcomm3d_b200.parallel.plan import RankPlan, build_my_plan, build_my_plan_from_spec
-    from spcomm3d_b200.utils import generate, native
+    from spcomm3d_b200.utils import affinity, generate, native
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -175,6 +175,8 @@ def run_ours(args):
     dev_index = pick_device(local_rank, world)
     torch.cuda.set_device(dev_index)
     device = torch.device("cuda", dev_index)
+    # pinned staging buffers and the threads that fill them: on the NUMA node of this rank's GPU
+    placement = affinity.bind_near_gpu(dev_index, local_rank, world)
     native.cuda()
     groups = None
     if world > 1:
@@ -341,7 +343,7 @@ def run_ours(args):
         "config": {"model": f"{args.gen} k={args.k} fp32 SDDMM then SpMM", "matrix": args.gen, "nnz": gnnz,
                    "k": args.k, "mesh": str(mesh), "variant": variant, "precision": "tf32 panels + fp32" if args.panels else "fp32", "global_batch": None, "seq_len": None,
                    "parallelism": f"mesh{mesh}", "l2": "operands larger than L2 at every N; no flush",
-                   "device_of_rank0": dev_index, "setup_s": round(setup_s, 1)},
+                   "device_of_rank0": dev_index, "numa_of_rank0": placement, "setup_s": round(setup_s, 1)},
     }
     if not verified:
         print(f"verification FAILED: max rel err sddmm {err_sd:.3e}, spmm {err_sp:.3e}", file=sys.stderr)

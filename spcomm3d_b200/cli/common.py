@@ -63,6 +63,8 @@ class Runtime:
         self.device = torch.device("cuda", local) if want_cuda else torch.device("cpu")
         if want_cuda:
             torch.cuda.set_device(self.device)
+            from ..utils import affinity
+            self.placement = affinity.bind_near_gpu(local, local, int(os.environ.get("LOCAL_WORLD_SIZE", self.world)))
         if self.world > 1:
             import torch.distributed as dist
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -221,3 +221,25 @@ def _heartbeat_and_fingerprint(rank, world):
 
 def test_plan_fingerprint_and_heartbeat():
     run_ranks(_heartbeat_and_fingerprint, 2)
+
+
+def test_numa_placement_from_a_fake_sysfs(tmp_path):
+    """The rank is restricted to the CPUs of its GPU's NUMA node; unknown node or device: nothing changes."""
+    import os
+    from spcomm3d_b200.utils import affinity
+    assert affinity.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    pci = "0000:1b:00.0"
+    (tmp_path / "bus/pci/devices" / pci).mkdir(parents=True)
+    (tmp_path / "bus/pci/devices" / pci / "numa_node").write_text("1\n")
+    mine = sorted(os.sched_getaffinity(0))
+    (tmp_path / "devices/system/node/node1").mkdir(parents=True)
+    (tmp_path / "devices/system/node/node1/cpulist").write_text(",".join(str(c) for c in mine) + ",100000\n")
+    info = affinity.bind_near(pci, sysfs=str(tmp_path), apply=False)
+    assert info == {"node": 1, "cpus": len(mine)}
+    if len(mine) >= 2:
+        half = affinity.bind_near(pci, sysfs=str(tmp_path), slot=1, nslots=2, apply=False)
+        assert half["cpus"] == len(mine) // 2
+    assert affinity.bind_near("0000:ff:00.0", sysfs=str(tmp_path), apply=False)["node"] is None
+    (tmp_path / "bus/pci/devices" / pci / "numa_node").write_text("-1\n")
+    assert affinity.bind_near(pci, sysfs=str(tmp_path), apply=False)["node"] is None
+    assert affinity.bind_near(None)["node"] is None
