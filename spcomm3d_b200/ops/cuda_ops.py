@@ -138,17 +138,22 @@ def build_spmm_wave_items(rowptr: np.ndarray, cls: np.ndarray, n_classes: int, l
     pcls = np.zeros(0, np.int64)
     first = np.zeros(0, np.int64)
     npieces = np.zeros(0, np.int64)
+    if lrows.size >= 1 << PIECE_SHIFT:
+        raise ValueError("too many split rows for the item encoding")
     if lrows.size:
         ldeg = deg[lrows]
-        starts = np.repeat(rowptr[lrows], ldeg)
-        slot_of = np.repeat(np.arange(lrows.size), ldeg)
-        within = np.arange(int(ldeg.sum())) - np.repeat(np.cumsum(ldeg) - ldeg, ldeg)
-        idx = starts + within                                  # nonzeros of the long rows, ascending
-        order = np.argsort(slot_of * 256 + cls[idx].astype(np.int64), kind="stable")
-        perm[idx] = idx[order]
-        c_sorted = cls[idx[order]].astype(np.int64)
+        lstart = np.cumsum(ldeg) - ldeg                        # first position of every long row in `idx`
+        slot_of = np.repeat(np.arange(lrows.size, dtype=np.int32), ldeg)
+        idx = np.arange(int(ldeg.sum()), dtype=np.int64)
+        idx += np.repeat(rowptr[lrows] - lstart, ldeg)         # nonzeros of the long rows, ascending
+        key = slot_of * np.int32(256)                          # < 2^28: the slot count is checked below
+        key += cls[idx]
+        order = np.argsort(key, kind="stable")
+        src = idx[order]
+        perm[idx] = src
+        key = key[order]                                       # slot_of is already grouped by row
+        c_sorted = key & np.int32(255)
         # runs of equal (row, class), cut every long_row nonzeros
-        key = slot_of * 256 + c_sorted                         # slot_of is already grouped by row
         run_start = np.flatnonzero(np.concatenate([[True], key[1:] != key[:-1]]))
         run_len = np.diff(np.append(run_start, key.size))
         nchunk = (run_len + long_row - 1) // long_row
@@ -160,17 +165,17 @@ def build_spmm_wave_items(rowptr: np.ndarray, cls: np.ndarray, n_classes: int, l
         npieces = np.bincount(p_slot, minlength=lrows.size)
         first = np.cumsum(npieces) - npieces
         p_num = np.arange(p_slot.size) - first[p_slot]
-        if lrows.size >= 1 << PIECE_SHIFT or int(npieces.max()) >= 1 << (31 - PIECE_SHIFT):
-            raise ValueError("too many split rows or pieces per row for the item encoding")
+        if int(npieces.max()) >= 1 << (31 - PIECE_SHIFT):
+            raise ValueError("too many pieces per row for the item encoding")
         pieces = np.stack([lrows[p_slot], idx[b_rel], idx[b_rel] + (e_rel - b_rel), p_slot + (p_num << PIECE_SHIFT)], axis=1)
-        pcls = c_sorted[b_rel]
+        pcls = c_sorted[b_rel].astype(np.int64)
     # class of a rows item: the largest class among its nonzeros
     rcls = np.zeros(rows_items.shape[0], np.int64)
     if rows_items.shape[0] and nnz:
         b, e = rowptr[rows_items[:, 0]], rowptr[rows_items[:, 1]]
         nonempty = e > b
         if nonempty.any():
-            cmax = np.maximum.reduceat(np.append(cls, 0).astype(np.int64), np.stack([b[nonempty], e[nonempty]], 1).ravel())[::2]
+            cmax = np.maximum.reduceat(np.append(cls, cls.dtype.type(0)), np.stack([b[nonempty], e[nonempty]], 1).ravel())[::2]
             rcls[nonempty] = cmax
     items = np.concatenate([pieces, rows_items])
     icls = np.concatenate([pcls, rcls])
