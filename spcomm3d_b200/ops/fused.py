@@ -317,8 +317,10 @@ class FusedSDDMM(_FusedBase):
             # the kernel walks the nonzeros class by class and stores its values in that order: `value_order`
             # is the storage order of this op's result (position in the plan's CSR order of every value)
             self.value_order = order
-            self._perm = (self._dev_i32(p.rowidx[order]), self._dev_i32(p.colidx[order]),
-                          torch.from_numpy(p.vals[order]).to(device=self.device, dtype=self.dtype))
+            order_dev = torch.from_numpy(order).to(self.device)    # the gathers run on the device
+            self._perm = (op.rowidx.index_select(0, order_dev), op.colidx.index_select(0, order_dev),
+                          op.vals.index_select(0, order_dev))
+            del order_dev
             a.rowidx, a.colidx, a.sval = (t.data_ptr() for t in self._perm)
             a.orig = None
             a.nnz_free = int(wave_nnz[0])
@@ -522,7 +524,7 @@ class FusedSpMM(_FusedBase):
             perm, items, first, npieces, class_items = cuda_ops.build_spmm_wave_items(p.rowptr, cls, n_waves + 1)
             self.sched = cuda_ops.SpmmSchedule(op.rowptr, arrays=(items, first, npieces))
             self._val_perm = torch.from_numpy(perm).to(self.device)
-            self._colidx = self._dev_i32(p.colidx[perm])
+            self._colidx = op.colidx.index_select(0, self._val_perm)
             self._vals = op.vals[self._val_perm]
             self._wave_items = self._dev_i32(class_items)
             a.n_waves, a.tiles_per_wave, a.wave_items = int(n_waves), int(tpw), self._wave_items.data_ptr()
