@@ -81,6 +81,41 @@ def bind_near(pci: str | None, sysfs: str = "/sys", slot: int = 0, nslots: int =
     return info
 
 
+def nvml_cpu_affinity(device_index: int, nvml=None) -> set[int]:
+    """CPUs that the driver names as close to a visible CUDA device (a read-only NVML query), or an empty set.
+    The device is found by its UUID, so a remapped CUDA_VISIBLE_DEVICES does not matter."""
+    try:
+        import torch
+        if nvml is None:
+            import pynvml as nvml
+            nvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        handle = nvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+        words = nvml.nvmlDeviceGetCpuAffinity(handle, ((os.cpu_count() or 64) + 63) // 64)
+    except Exception:   # no driver, no NVML, an old torch without uuid: placement is best effort
+        return set()
+    return {64 * w + b for w, word in enumerate(words) for b in range(64) if int(word) >> b & 1}
+
+
+def bind_to(cpus: set[int], slot: int = 0, nslots: int = 1, apply: bool = True) -> int:
+    """Restricts this process to the slot-th of nslots shares of `cpus` (those it may already use);
+    returns the number of CPUs it ends up with, 0 = nothing changed."""
+    if not cpus or not hasattr(os, "sched_getaffinity"):
+        return 0
+    allowed = sorted(cpus & os.sched_getaffinity(0))
+    if nslots > 1 and len(allowed) >= nslots:
+        per = len(allowed) // nslots
+        allowed = allowed[slot * per:(slot + 1) * per]
+    if not allowed:
+        return 0
+    if apply:
+        try:
+            os.sched_setaffinity(0, allowed)
+        except OSError:
+            return 0
+    return len(allowed)
+
+
 def bind_near_gpu(device_index: int, local_rank: int = 0, local_world: int = 1) -> dict:
     """`bind_near` for a CUDA device; SP3_NUMA_BIND=0 switches it off.  Ranks of one node that share a NUMA
     node split its CPUs: the share is chosen from the local rank, assuming the ranks are spread evenly over
@@ -92,4 +127,12 @@ def bind_near_gpu(device_index: int, local_rank: int = 0, local_world: int = 1) 
     except OSError:
         n_nodes = 1
     per_node = max(1, -(-local_world // max(n_nodes, 1)))
-    return bind_near(pci_address(device_index), slot=local_rank % per_node, nslots=per_node)
+    slot = local_rank % per_node
+    info = bind_near(pci_address(device_index), slot=slot, nslots=per_node)
+    if info["node"] is None:
+        # sysfs names no node (a container without it): ask the driver which CPUs are close to the GPU; a set
+        # that covers every CPU of the machine says nothing and is left alone
+        cpus = nvml_cpu_affinity(device_index)
+        if cpus and len(cpus) < (os.cpu_count() or 0):
+            info = {"node": "nvml", "cpus": bind_to(cpus, slot, per_node)}
+    return info

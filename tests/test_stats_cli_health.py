@@ -243,3 +243,27 @@ def test_numa_placement_from_a_fake_sysfs(tmp_path):
     (tmp_path / "bus/pci/devices" / pci / "numa_node").write_text("-1\n")
     assert affinity.bind_near(pci, sysfs=str(tmp_path), apply=False)["node"] is None
     assert affinity.bind_near(None)["node"] is None
+
+
+def test_cpu_affinity_from_a_fake_nvml(monkeypatch):
+    """Without a NUMA node in sysfs the CPUs close to the GPU come from the driver's affinity mask."""
+    import os
+    import types
+    import torch
+    from spcomm3d_b200.utils import affinity
+
+    class FakeNvml:
+        def nvmlDeviceGetHandleByUUID(self, uuid):
+            assert uuid == "GPU-1234"
+            return "h"
+
+        def nvmlDeviceGetCpuAffinity(self, handle, nwords):
+            return [0b1010] + [0] * (nwords - 2) + ([1] if nwords > 1 else [])
+
+    monkeypatch.setattr(torch.cuda, "get_device_properties", lambda i: types.SimpleNamespace(uuid="1234"))
+    cpus = affinity.nvml_cpu_affinity(0, nvml=FakeNvml())
+    nwords = ((os.cpu_count() or 64) + 63) // 64
+    assert cpus == ({1, 3} | ({64 * (nwords - 1)} if nwords > 1 else set()))
+    mine = sorted(os.sched_getaffinity(0))
+    assert affinity.bind_to(set(mine), apply=False) == len(mine)
+    assert affinity.bind_to({10 ** 6}, apply=False) == 0 and affinity.bind_to(set()) == 0
