@@ -772,6 +772,9 @@ struct FusedSpmmArgs {
     // owned part of a hub row is computed while the pulls are in flight.
     int n_waves, tiles_per_wave;
     const int* wave_items;
+    // ticket -> tile of needed X rows (null: ascending).  The host starts every rank at the peer after itself
+    // on its mesh line, so that the ranks of a line read from different owners at any one time.
+    const int* pull_order;
 };
 
 // Rows I own go straight into the result (Y = beta*Y + my partial; the owners' FINISH phase then adds what
@@ -926,7 +929,7 @@ __global__ void __launch_bounds__(256, (R <= 2 ? 4 : 2)) fused_spmm_kernel(const
             gate.c = c;
             gate.side[0] = {a.x_src, reinterpret_cast<float4*>(Xv + (long long)a.n_owned_x * ldx_v), a.n_recv_x};
             gate.side[1] = {nullptr, nullptr, 0};
-            gate.order = nullptr;
+            gate.order = a.pull_order;
             gate.limit = wave_limit;
             gate.ld_v = ldx_v;
             gate.nvec = a.nvec; gate.tile_rows = PULL_ROWS; gate.n_pull = n_pull; gate.tiles1 = 0;

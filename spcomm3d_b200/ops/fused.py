@@ -67,7 +67,8 @@ class _SpmmArgs(C.Structure):
                 ("crows", P), ("y_dst", P), ("parity_off_v", C.c_longlong), ("Y", P),
                 ("ldy", C.c_longlong), ("beta", C.c_double), ("cptr", P), ("cslot", P), ("slots", P),
                 ("lds", C.c_longlong), ("atomic", C.c_int), ("red_v4", C.c_int), ("crow_flag", P),
-                ("pull", _PullConfig), ("n_waves", C.c_int), ("tiles_per_wave", C.c_int), ("wave_items", P)]
+                ("pull", _PullConfig), ("n_waves", C.c_int), ("tiles_per_wave", C.c_int), ("wave_items", P),
+                ("pull_order", P)]
 
 
 _checked_layout = False
@@ -120,6 +121,19 @@ def _peer_ranks(plan, side: str):
     if side == "col":
         return [m.rank_of(i, y, z) for i in range(m.X)]
     return [m.rank_of(x, y, k) for k in range(m.Z)]
+
+
+def _tiles_by_peer_distance(side, n_tiles: int, tile_rows: int) -> np.ndarray:
+    """Tiles of a side's receive list in the order they are pulled: first the tiles whose rows belong to the
+    peer after me on the mesh line, then the next peer, and so on round the line.  In ascending order every
+    rank of a line would start at peer 0 and move on together, so that at any time one owner serves all
+    readers of the line through its one link while the others sit idle.  (A tile that straddles two peers goes
+    with the peer of its first row.)  SP3_FUSED_ROTATE=0 keeps the ascending order."""
+    tiles = np.arange(n_tiles, dtype=np.int64)
+    if n_tiles == 0 or side.npeers <= 2 or os.environ.get("SP3_FUSED_ROTATE", "1") != "1":
+        return tiles
+    peer = side.recv_peer[tiles * tile_rows].astype(np.int64)
+    return np.argsort((peer - side.me - 1) % side.npeers, kind="stable")
 
 
 class _FusedBase:
@@ -378,7 +392,10 @@ class FusedSDDMM(_FusedBase):
         target_waves = max(1, min(MAX_WAVES, target_waves))
         n_a, n_b = -(-n_recv_a // self.tile_rows), -(-p.col.n_recv // self.tile_rows)
         n_pull = n_a + n_b
-        key = np.concatenate([(np.arange(n_a) + 0.5) / max(n_a, 1), (np.arange(n_b) + 0.5) / max(n_b, 1)])
+        pos_a, pos_b = np.empty(n_a, np.int64), np.empty(n_b, np.int64)   # place of every tile in its side's sequence
+        pos_a[_tiles_by_peer_distance(p.row, n_a, self.tile_rows)] = np.arange(n_a)
+        pos_b[_tiles_by_peer_distance(p.col, n_b, self.tile_rows)] = np.arange(n_b)
+        key = np.concatenate([(pos_a + 0.5) / max(n_a, 1), (pos_b + 0.5) / max(n_b, 1)])
         code = np.concatenate([np.arange(n_a, dtype=np.int64) | (1 << 30), np.arange(n_b, dtype=np.int64)])
         seq = np.argsort(key, kind="stable")
         pull_order = code[seq]
@@ -510,7 +527,7 @@ class FusedSpMM(_FusedBase):
         # nonzeros of long rows are sorted so that their owned columns come first: the kernel then works on
         # what is there while the X rows arrive.  The re-ordered column indices and values are private copies
         # (`_val_perm` maps them to the op's CSR arrays; `refresh_values` follows a change of the values).
-        self._val_perm, a.n_waves, a.tiles_per_wave, a.wave_items = None, 0, 0, None
+        self._val_perm, a.n_waves, a.tiles_per_wave, a.wave_items, a.pull_order = None, 0, 0, None, None
         if os.environ.get("SP3_FUSED_SPMM_WAVES") == "0":   # tuning: no overlap, compute after the last pull
             overlap = False
         if overlap and p.col.n_recv > 0 and p.nnz > 0:
@@ -518,9 +535,12 @@ class FusedSpMM(_FusedBase):
             n_pull = -(-p.col.n_recv // self.tile_rows)
             tpw = -(-n_pull // target)
             n_waves = -(-n_pull // tpw)
+            pull_order = _tiles_by_peer_distance(p.col, n_pull, self.tile_rows)
+            ticket_of = np.empty(n_pull, np.int64)
+            ticket_of[pull_order] = np.arange(n_pull)
             cls = np.zeros(p.nnz, np.int8)
             rem = p.colidx >= p.col.n_owned
-            cls[rem] = ((p.colidx[rem] - p.col.n_owned) // self.tile_rows) // tpw + 1
+            cls[rem] = ticket_of[(p.colidx[rem] - p.col.n_owned) // self.tile_rows] // tpw + 1
             perm, items, first, npieces, class_items = cuda_ops.build_spmm_wave_items(p.rowptr, cls, n_waves + 1)
             self.sched = cuda_ops.SpmmSchedule(op.rowptr, arrays=(items, first, npieces))
             self._val_perm = torch.from_numpy(perm).to(self.device)
@@ -528,6 +548,8 @@ class FusedSpMM(_FusedBase):
             self._vals = op.vals[self._val_perm]
             self._wave_items = self._dev_i32(class_items)
             a.n_waves, a.tiles_per_wave, a.wave_items = int(n_waves), int(tpw), self._wave_items.data_ptr()
+            self._pull_order = self._dev_i32(pull_order)
+            a.pull_order = self._pull_order.data_ptr()
         else:
             self.sched = cuda_ops.SpmmSchedule(op.rowptr)
             self._colidx, self._vals = op.colidx, op.vals

@@ -198,3 +198,28 @@ def test_spmm_wave_items_cover_every_nonzero_once_in_class_order():
     pieces = it2[it2[:, 3] >= 0]
     got = sorted((int(w) & ((1 << PIECE_SHIFT) - 1), int(w) >> PIECE_SHIFT) for w in pieces[:, 3])
     assert got == sorted((lr, j) for lr in range(len(n2)) for j in range(int(n2[lr])))
+
+
+def test_pull_order_starts_at_the_next_peer_of_the_line(monkeypatch):
+    """Ranks of a mesh line pull from different owners at any one time: rank m starts with peer m + 1."""
+    import types
+    from spcomm3d_b200.ops.fused import _tiles_by_peer_distance
+    npeers, tile_rows = 4, 8
+    counts = {0: 40, 1: 24, 3: 16}                       # rows needed from each peer by rank 2
+    recv_peer = np.concatenate([np.full(c, q, np.int32) for q, c in counts.items()])
+    side = types.SimpleNamespace(npeers=npeers, me=2, recv_peer=recv_peer)
+    n_tiles = -(-recv_peer.size // tile_rows)
+    order = _tiles_by_peer_distance(side, n_tiles, tile_rows)
+    assert sorted(order.tolist()) == list(range(n_tiles))
+    peers_in_order = recv_peer[order * tile_rows].tolist()
+    assert peers_in_order == [3] * 2 + [0] * 5 + [1] * 3           # 3, then round the line: 0, 1
+    first = []
+    for m in range(4):
+        rp = np.repeat(np.array([q for q in range(4) if q != m], np.int32), 16)
+        sm = types.SimpleNamespace(npeers=4, me=m, recv_peer=rp)
+        first.append(int(rp[_tiles_by_peer_distance(sm, 6, 8)[0] * 8]))
+    assert first == [1, 2, 3, 0]                                   # four ranks, four different first owners
+    two = types.SimpleNamespace(npeers=2, me=0, recv_peer=np.ones(32, np.int32))
+    assert _tiles_by_peer_distance(two, 4, 8).tolist() == [0, 1, 2, 3]
+    monkeypatch.setenv("SP3_FUSED_ROTATE", "0")
+    assert _tiles_by_peer_distance(side, n_tiles, tile_rows).tolist() == list(range(n_tiles))
