@@ -318,8 +318,8 @@ class FusedSDDMM(_FusedBase):
         others = [r for r in fiber if r != self.rank] if Z > 1 else []
         self._fill_comm(a.comm, read_from, readers, others, others)
         a.nnz = p.nnz
-        # nonzeros whose B row is owned first (computable while the pulls are in flight), the others after
-        # them; both parts keep the row-sorted order, results are stored at their position in the plan's order
+        # with rows to pull, the nonzeros are re-ordered by the pull wave that completes them (`_plan_waves`):
+        # what needs no pulled row is computed while the pulls are in flight
         n_recv_a = p.row.n_recv if self.stage_a else 0
         a.n_recv_a, a.a_src = n_recv_a, self.a_src.data_ptr()
         a.A_stage = self._A_full.data_ptr() + p.row.n_owned * self.row_bytes
