@@ -267,3 +267,22 @@ def test_cpu_affinity_from_a_fake_nvml(monkeypatch):
     mine = sorted(os.sched_getaffinity(0))
     assert affinity.bind_to(set(mine), apply=False) == len(mine)
     assert affinity.bind_to({10 ** 6}, apply=False) == 0 and affinity.bind_to(set()) == 0
+
+
+def test_ranks_are_spread_over_the_visible_gpus(monkeypatch):
+    """Fewer ranks than GPUs: rank r runs on device r * visible / world, so that neighbouring ranks do not
+    share a PCIe uplink; SP3_DEVICE_MAP=dense or a count that does not divide keeps rank r on device r."""
+    import importlib.util
+    import pathlib
+    import torch
+    spec = importlib.util.spec_from_file_location("sp3_bench", pathlib.Path(__file__).resolve().parent.parent / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    monkeypatch.setattr(torch.cuda, "device_count", lambda: 8)
+    monkeypatch.delenv("SP3_DEVICE_MAP", raising=False)
+    assert [bench.pick_device(r, 4) for r in range(4)] == [0, 2, 4, 6]
+    assert [bench.pick_device(r, 2) for r in range(2)] == [0, 4]
+    assert [bench.pick_device(r, 8) for r in range(8)] == list(range(8))
+    assert [bench.pick_device(r, 3) for r in range(3)] == [0, 1, 2]
+    monkeypatch.setenv("SP3_DEVICE_MAP", "dense")
+    assert [bench.pick_device(r, 4) for r in range(4)] == [0, 1, 2, 3]
