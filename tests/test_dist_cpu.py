@@ -1,5 +1,7 @@
 """Distributed CPU plumbing: gloo ranks, fp64, every variant against the
 single-process oracle, with non-owned rows poisoned before each run."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -34,6 +36,9 @@ def _check_rank(rank, world, meshstr, kernel, variant, k, from_file):
     z = groups.coords[2]
     if kernel == "sddmm":
         op = DistSDDMM(plan, groups, k, torch.float64, "cpu", variant)
+        # "sparse" on a mesh with a plane moves A and B rows in one exchange (not with the p2p transport)
+        combined = variant == "sparse" and mesh.xy_size > 1 and os.environ.get("SP3_TRANSPORT", "alltoall") == "alltoall"
+        assert (op.exAB is not None) == combined
         op.fill_owned(op.A_owned, plan.row.owned_gids, seed=5, stream=1)
         op.fill_owned(op.B_owned, plan.col.owned_gids, seed=5, stream=2)
         for _ in range(2):
