@@ -60,9 +60,9 @@ def parse_args():
     return ap.parse_args()
 
 
-# Fastest mesh per GPU count among those measured on this matrix (fused variant, SDDMM + SpMM):
-# N=2: 1x2x1 1.07 ms vs 2x1x1 1.17, 1x1x2 1.23 (R-MAT-20); N=4: 2x2x1 2.49 ms vs 1x2x2 2.70, 2x1x2 2.94;
-# N=8: 2x2x2 1.99 ms vs 4x2x1 2.05 (R-MAT-22).
+# Fastest mesh per GPU count among those measured on R-MAT-22, k = 128 (fused variant, SDDMM + SpMM per step):
+# N=2: 1x2x1 3.64 ms vs 2x1x1 3.79, 1x1x2 4.55; N=4: 2x2x1 2.17 ms vs 4x1x1 2.41, 1x2x2 2.43, 2x1x2 2.67;
+# N=8: 2x2x2 1.55 ms vs 4x2x1 2.10, 1x1x8 3.31.
 MEASURED_MESH = {1: (1, 1, 1), 2: (1, 2, 1), 4: (2, 2, 1), 8: (2, 2, 2)}
 
 
